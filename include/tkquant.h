@@ -1,0 +1,154 @@
+/*
+ * tkquant.h -- C ABI of libtkquant.so: B200 (sm_100a) quantization casts.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues exactly one
+ * kernel on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream) and returns without synchronising.  Nothing here allocates, frees or
+ * keeps a pointer after the launch.
+ *
+ * Return value: 0 on success; a positive cudaError_t if the launch failed; a
+ * negative TKQ_E_* code when the arguments describe a case the library does not
+ * implement (nothing was launched).  tkq_last_error_string() explains the last
+ * non-zero return of the calling thread.
+ *
+ * Each function names the interface of the reference project (deepseek-ai
+ * TileKernels; paths relative to that project) whose kernel launch it replaces.
+ *
+ * Scale-factor ("SF") storage, shared by all entry points
+ * (reference: tile_kernels/quant/common.py:130-165 get_sf_shape/alloc_scaling_factors,
+ *  :219-244 load_sf/store_sf):
+ *   row-major fp32        sf[m * sf_stride + k]                      (float)
+ *   TKQ_SF_COL_MAJOR      sf[k * sf_stride + m]                      (float)
+ *   + TKQ_SF_UE8M0        sf[(k / 4) * sf_stride + 4 * m + k % 4]    (uint8 exponent bytes)
+ * with m = token-block index, k = channel-block index and sf_stride in elements
+ * of the stated type.  In packed mode the library also zeroes the bytes of a
+ * 4-group word that lie beyond the last channel block.
+ */
+#ifndef TKQUANT_H_
+#define TKQUANT_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of `x` */
+#define TKQ_DT_BF16 0
+#define TKQ_DT_FP32 1
+
+/* output formats */
+#define TKQ_FMT_E4M3 0 /* 1 byte per element (float8_e4m3fn) */
+#define TKQ_FMT_E2M1 1 /* 2 elements per byte, even index in the low nibble */
+#define TKQ_FMT_E5M6 2 /* 8 elements in 3 little-endian uint32 words */
+
+/* flag bits */
+#define TKQ_ROUND_SF 1u     /* round the scale up to a power of two */
+#define TKQ_SF_COL_MAJOR 2u /* column-major scale storage */
+#define TKQ_SF_UE8M0 4u     /* exponent bytes, four per 32-bit word; needs TKQ_SF_COL_MAJOR */
+#define TKQ_SF_ONLY 8u      /* compute and store scales only; `out` is not touched */
+#define TKQ_CAST_ONLY 16u   /* read row-major fp32 scales from `sf`, store data only */
+
+/* negative return codes */
+#define TKQ_E_BAD_ARG (-1)     /* null pointer, negative size, unknown enum */
+#define TKQ_E_UNSUPPORTED (-2) /* shape/flag combination not implemented */
+#define TKQ_E_ALIGNMENT (-3)   /* pointer or stride not aligned as documented */
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int tkq_version(void);
+
+/* Text for the calling thread's last non-zero return value (never NULL). */
+const char* tkq_last_error_string(void);
+
+/*
+ * Device-side failure flag.  The tile kernels (per-block, per-channel) wait for their
+ * shared-memory tile with a bounded number of polls; a kernel that runs out of polls
+ * raises a flag and returns without writing.  This call synchronises the device,
+ * returns 1 if the flag was raised since the last call (and clears it), 0 if not,
+ * -1 if the flag could not be read.  No counterpart in the reference.
+ */
+int tkq_device_error(void);
+
+/*
+ * Per-token cast to FP8 e4m3 or FP4 e2m1: one scale per (1 x num_per_channels) group.
+ * Replaces the launch in tile_kernels/quant/per_token_cast_kernel.py:208-209
+ * (kernel body :72-154; per_token_cast / _with_sf_only / _with_precomputed_sf, :223-302).
+ *
+ *   x             [num_tokens, hidden] bf16 or fp32, row stride x_row_stride elements, unit column stride
+ *   num_per_channels  16, 32, 64, 128, or == hidden (one scale per token; hidden % 64 == 0)
+ *   out           e4m3: [num_tokens, hidden] bytes; e2m1: [num_tokens, hidden / 2] bytes; contiguous
+ *   sf            scale storage as described above (m = token, k = group); read with TKQ_CAST_ONLY
+ * Alignment: x, out 16-byte aligned, hidden and x_row_stride multiples of 16 elements.
+ */
+int tkq_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int64_t x_row_stride, int fmt,
+                       int64_t num_per_channels, unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream);
+
+/*
+ * Per-token cast to E5M6 (12-bit codes, one scale per token, maximum 65024, clamp 1e-4).
+ * Replaces the launch in tile_kernels/quant/per_token_cast_to_e5m6_kernel.py:209-210
+ * (kernel :108-154, float_to_e5m6 :33-64).
+ *
+ *   x      [num_tokens, hidden] bf16 or fp32, hidden % 8 == 0
+ *   out    [num_tokens, hidden / 8 * 3] uint32 words, contiguous
+ *   sf     one scale per token: k = 0 in the formulas above
+ */
+int tkq_per_token_cast_e5m6(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int64_t x_row_stride,
+                            unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream);
+
+/*
+ * Per-block cast: one scale per (block_m x block_k) tile, block sizes 32 or 128.
+ * Replaces the launch in tile_kernels/quant/per_block_cast_kernel.py:191-192
+ * (kernel :97-136; per_block_cast / _with_sf_only / _with_precomputed_sf, :205-276).
+ *
+ *   x      [num_tokens, hidden] bf16 or fp32, contiguous, hidden % 64 == 0
+ *   out    e4m3 [num_tokens, hidden] or e2m1 [num_tokens, hidden / 2] bytes
+ *   sf     m = token-block, k = channel-block
+ */
+int tkq_per_block_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int fmt, int block_m,
+                       int block_k, unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream);
+
+/*
+ * Per-channel cast to e4m3: one scale per (128 tokens x 1 channel).
+ * Replaces the launch in tile_kernels/quant/per_channel_cast_fused_kernel.py:200-201
+ * (kernel :50-132) for the plain-input case reached through
+ * tile_kernels/quant/per_channel_cast_kernel.py:8-28.
+ *
+ *   x      [num_tokens, hidden] bf16 or fp32, contiguous, num_tokens % 128 == 0, hidden % 64 == 0
+ *   out    [num_tokens, hidden] bytes
+ *   sf     [num_tokens / 128, hidden] fp32 row-major, contiguous
+ * flags: TKQ_ROUND_SF only.
+ */
+int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, unsigned flags, void* out,
+                         void* sf, void* stream);
+
+/*
+ * Fused SwiGLU + per-token e4m3 cast: y = silu(x[:, :hidden]) * x[:, hidden:] in fp32
+ * (times an optional per-row weight), then the per-token cast of y.
+ * Replaces the launch in tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:255-256
+ * (kernel :61-170).
+ *
+ *   x                  [num_tokens, 2 * hidden] bf16 or fp32, contiguous, hidden % 128 == 0
+ *   num_per_channels   128 or hidden
+ *   pos_to_token_topk  optional int32[num_tokens]; with topk_weights (fp32, flat) gives the row
+ *                      weight topk_weights[pos]; a negative position leaves the weight undefined
+ *                      in the reference -- here it is 0
+ *   pos_to_expert      optional int32[num_tokens]; rows with a negative entry are skipped
+ *                      (neither out nor sf is written for them)
+ *   swiglu_clamp       < 0: no clamp; else gate = min(gate, c), up = clamp(up, -c, c)
+ *   clamped_count      optional int64[3], atomically incremented by the numbers of
+ *                      gate > c, up > c, up < -c (needs swiglu_clamp >= 0)
+ *   sf_clamp_min       < 0: the format default 1e-4; else the lower clamp of the group maximum
+ *   num_sms            > 0 limits the grid of the counting variant to num_sms * 4 blocks
+ *                      (tile_kernels/config.py:13-23); 0 = all SMs
+ *   out                [num_tokens, hidden] bytes
+ */
+int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden,
+                                          int64_t num_per_channels, const int32_t* pos_to_token_topk,
+                                          const float* topk_weights, const int32_t* pos_to_expert, float swiglu_clamp,
+                                          long long* clamped_count, float sf_clamp_min, int num_sms, unsigned flags,
+                                          void* out, void* sf, int64_t sf_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TKQUANT_H_ */

@@ -1,0 +1,212 @@
+"""CPU oracle for the quantization casts -- TEST INFRASTRUCTURE ONLY.
+
+Only tests/, the smoke check and the CPU-baseline legs of bench.py import this
+package; tilekernels_b200 never does.  The arithmetic lives in tkq_oracle.c
+(a restatement of the reference's tile_kernels/torch/{cast,cast_e5m6,swiglu}.py,
+cited function by function there).  This wrapper hands torch CPU tensors to it
+and lays the scale factors out the way the reference returns them
+(tile_kernels/torch/cast.py:199-219, cast_e5m6.py:23-34,190-216), so that a
+test can compare dtype, shape, strides and bytes.
+"""
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from .build import LIB, build
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB):
+            build()
+        _lib = ctypes.CDLL(LIB)
+        _lib.tkq_expf.restype = ctypes.c_float
+        _lib.tkq_expf.argtypes = [ctypes.c_float]
+    return _lib
+
+
+def _ceil_div(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+def _align(a: int, b: int) -> int:
+    return _ceil_div(a, b) * b
+
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+_FMT = {'e4m3': 0, 'e2m1': 1}
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+
+
+def _rows(x: torch.Tensor):
+    assert x.device.type == 'cpu' and x.dim() == 2 and x.dtype in _DT
+    if x.shape[1] > 0 and x.stride(1) != 1:
+        x = x.contiguous()
+    return x
+
+
+def format_sf(bits: torch.Tensor, col_major: bool, packed_ue8m0: bool) -> torch.Tensor:
+    """Row-major int32 scale bits [nm, nk] -> the reference's returned scale tensor.
+
+    row-major:   fp32 [nm, nk]
+    col-major:   fp32 [nm, nk] with strides (1, align(nm, 4)), padding zero
+    packed:      int32 [nm, ceil(nk/4)] with strides (1, align(nm, 4)); byte b of
+                 word k is the exponent byte of group 4k+b, padding zero
+    (tile_kernels/torch/cast.py:199-219)
+    """
+    nm, nk = bits.shape
+    if not col_major:
+        return bits.view(torch.float32)
+    nm_pad = _align(nm, 4)
+    if packed_ue8m0:
+        nkw = _ceil_div(nk, 4)
+        exp_bytes = torch.zeros((nm, nkw * 4), dtype=torch.uint8)
+        exp_bytes[:, :nk] = (bits >> 23).to(torch.uint8)
+        words = exp_bytes.view(torch.int32)  # [nm, nkw]
+        storage = torch.zeros((nkw, nm_pad), dtype=torch.int32)
+        storage[:, :nm] = words.T
+        return storage.T[:nm, :]
+    storage = torch.zeros((nk, nm_pad), dtype=torch.float32)
+    storage[:, :nm] = bits.view(torch.float32).T
+    return storage.T[:nm, :]
+
+
+def cast(x: torch.Tensor, fmt: str, block_size=(32, 32), sf: Optional[torch.Tensor] = None, round_sf: bool = False,
+         use_tma_aligned_col_major_sf: bool = False, use_packed_ue8m0: bool = False,
+         clamp_min: Optional[float] = None):
+    """Same contract as the reference's tile_kernels.torch.cast (cast.py:62-221) for plain
+    bf16/fp32 inputs.  Returns `out` when `sf` is given, else `(out, out_sf)`."""
+    x = _rows(x)
+    T, H = x.shape
+    bm, bk = block_size
+    is_fp4 = fmt == 'e2m1'
+    out_dtype = torch.int8 if is_fp4 else torch.float8_e4m3fn
+    out = torch.empty((T, H // 2 if is_fp4 else H), dtype=torch.uint8)
+    nm, nk = _ceil_div(T, bm), _ceil_div(H, bk)
+    bits = torch.zeros((nm, nk), dtype=torch.int32)
+    sf_ptr = None
+    if sf is not None:
+        assert not use_packed_ue8m0 and not use_tma_aligned_col_major_sf
+        assert tuple(sf.shape) == (nm, nk) and sf.dtype == torch.float32
+        sf_c = sf.contiguous()
+        sf_ptr = _vp(sf_c.data_ptr())
+    if T > 0:
+        rc = lib().tkqo_cast(_vp(x.data_ptr()), _DT[x.dtype], _i64(T), _i64(H), _i64(x.stride(0)), _FMT[fmt],
+                             int(bm), int(bk), int(round_sf),
+                             ctypes.c_float(-1.0 if clamp_min is None else clamp_min), sf_ptr,
+                             _vp(out.data_ptr()), _vp(bits.data_ptr()))
+        assert rc == 0, f'oracle cast failed ({rc})'
+    out = out.view(out_dtype)
+    if sf is not None:
+        return out
+    if T == 0:  # shapes of the empty case, cast.py:109-123
+        if use_packed_ue8m0:
+            return out, torch.empty((_ceil_div(nk, 4), 0), dtype=torch.int32).T
+        if use_tma_aligned_col_major_sf:
+            return out, torch.empty((nk, 0), dtype=torch.float32).T
+        return out, torch.empty((0, nk), dtype=torch.float32)
+    return out, format_sf(bits, use_tma_aligned_col_major_sf, use_packed_ue8m0)
+
+
+def cast_back(x, fmt: str, block_size=(32, 32)) -> torch.Tensor:
+    """Dequantise (q, sf) to fp32 or bf16 (tile_kernels/torch/cast.py:40-59)."""
+    q, sf = x
+    is_fp4 = q.dtype == torch.int8
+    T = q.shape[0]
+    H = q.shape[1] * (2 if is_fp4 else 1)
+    bm, bk = block_size
+    sf32 = sf_to_float(sf)[:, :_ceil_div(H, bk)].contiguous()
+    out = torch.empty((T, H), dtype=torch.float32)
+    if T > 0:
+        lib().tkqo_cast_back(_vp(q.contiguous().data_ptr()), 1 if is_fp4 else 0, _i64(T), _i64(H), int(bm), int(bk),
+                             _vp(sf32.data_ptr()), _vp(out.data_ptr()))
+    return out if fmt == 'fp32' else out.bfloat16()
+
+
+def sf_to_float(sf: torch.Tensor) -> torch.Tensor:
+    """fp32 scales unchanged; packed int32 ue8m0 words -> fp32 [nm, 4*words] (cast.py:28-37)."""
+    if sf.dtype == torch.float32:
+        return sf
+    assert sf.dtype == torch.int32
+    dense = torch.empty(sf.shape, dtype=sf.dtype)
+    dense.copy_(sf)
+    b = dense.view(torch.uint8).to(torch.int32)
+    return (b << 23).view(torch.float32)
+
+
+def cast_to_e5m6(x: torch.Tensor, num_per_channels: int, use_tma_aligned_col_major_sf: bool = False,
+                 round_sf: bool = False, use_packed_ue8m0: bool = False):
+    """Same contract as tile_kernels.torch.cast_to_e5m6 (cast_e5m6.py:135-218)."""
+    x = _rows(x)
+    T, H = x.shape
+    g = num_per_channels
+    assert H % g == 0 and H % 8 == 0 and g % 8 == 0
+    ng = H // g
+    words = torch.empty((T, H // 8 * 3), dtype=torch.int32)
+    sfw = torch.zeros((T, ng), dtype=torch.int32)
+    if T > 0:
+        rc = lib().tkqo_cast_e5m6(_vp(x.data_ptr()), _DT[x.dtype], _i64(T), _i64(H), _i64(x.stride(0)), _i64(g),
+                                  int(round_sf), int(use_packed_ue8m0), _vp(words.data_ptr()), _vp(sfw.data_ptr()))
+        assert rc == 0
+    packed = words.view(torch.uint8)
+    if use_packed_ue8m0:
+        ngw = _ceil_div(ng, 4)
+        eb = torch.zeros((T, ngw * 4), dtype=torch.uint8)
+        eb[:, :ng] = sfw.to(torch.uint8)
+        sf_out = eb.view(torch.int32)
+    else:
+        sf_out = sfw.view(torch.float32)
+    if use_tma_aligned_col_major_sf:  # cast_e5m6.py:23-34
+        storage = torch.zeros((sf_out.shape[1], _align(T, 4)), dtype=sf_out.dtype)
+        storage[:, :T] = sf_out.T
+        sf_out = storage.T[:T, :]
+    return packed, sf_out
+
+
+def swiglu_forward(x: torch.Tensor, pos_to_token_topk: Optional[torch.Tensor] = None,
+                   topk_weights: Optional[torch.Tensor] = None, swiglu_clamp_value: Optional[float] = None,
+                   clamped_count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Same contract as tile_kernels.torch.swiglu_forward (swiglu.py:9-88); exp() is tkq_expf."""
+    assert x.dim() == 2 and x.is_contiguous() and x.dtype in _DT
+    T, H2 = x.shape
+    H = H2 // 2
+    y = torch.empty((T, H), dtype=torch.float32)
+    pos_ptr = w_ptr = cnt_ptr = None
+    if pos_to_token_topk is not None:
+        pos = pos_to_token_topk.to(torch.int32).contiguous()
+        w = topk_weights.to(torch.float32).contiguous()
+        pos_ptr, w_ptr = _vp(pos.data_ptr()), _vp(w.data_ptr())
+    if clamped_count is not None:
+        assert clamped_count.dtype == torch.int64 and clamped_count.is_contiguous()
+        cnt_ptr = _vp(clamped_count.data_ptr())
+    if T > 0:
+        lib().tkqo_swiglu_forward(_vp(x.data_ptr()), _DT[x.dtype], _i64(T), _i64(H),
+                                  ctypes.c_float(-1.0 if swiglu_clamp_value is None else swiglu_clamp_value),
+                                  cnt_ptr, pos_ptr, w_ptr, _vp(y.data_ptr()))
+    return y
+
+
+def expf(x: torch.Tensor) -> torch.Tensor:
+    x = x.contiguous().float()
+    y = torch.empty_like(x)
+    lib().tkqo_expf_array(_vp(x.data_ptr()), _vp(y.data_ptr()), _i64(x.numel()))
+    return y
+
+
+def convert_array(x: torch.Tensor, fmt: str) -> torch.Tensor:
+    """Element converters for the unit tests: fp32 -> codes ('e4m3' clamps to +-448 first)."""
+    x = x.contiguous().float()
+    if fmt == 'e5m6':
+        y = torch.empty(x.shape, dtype=torch.int32)
+        lib().tkqo_f32_to_e5m6_array(_vp(x.data_ptr()), _vp(y.data_ptr()), _i64(x.numel()))
+        return y
+    y = torch.empty(x.shape, dtype=torch.uint8)
+    fn = lib().tkqo_f32_to_e4m3_array if fmt == 'e4m3' else lib().tkqo_f32_to_e2m1_array
+    fn(_vp(x.data_ptr()), _vp(y.data_ptr()), _i64(x.numel()))
+    return y

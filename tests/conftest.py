@@ -1,0 +1,28 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line('markers', 'gpu: needs a CUDA device (B200); run with -m gpu')
+
+
+@pytest.fixture(scope='session')
+def oracle():
+    """The CPU oracle (builds oracle/libtkq_oracle.so on first use)."""
+    import oracle as _oracle
+    _oracle.lib()
+    return _oracle
+
+
+@pytest.fixture(scope='session')
+def cuda_device():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail('a test marked gpu ran without a CUDA device')
+    return torch.device('cuda', 0)

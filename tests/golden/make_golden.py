@@ -1,0 +1,203 @@
+"""Generate the golden fixtures of this folder from the reference implementation.
+
+Run in a container that has the reference checkout (it is imported, never copied):
+
+    PYTHONPATH=/path/to/TileKernels python tests/golden/make_golden.py
+
+It calls the reference's own PyTorch implementation (tile_kernels.torch.cast,
+cast_to_e5m6, swiglu_forward, cast_back) on seeded CPU inputs and stores inputs and
+outputs as raw bytes in small .npz files, plus SHA-256 digests of the reference
+outputs for reduced-row versions of the five benchmark workloads
+(config_digests.json).  The tests compare the CPU oracle and the CUDA kernels
+with these files; nothing at test time needs the reference.
+"""
+import hashlib
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from tile_kernels.torch import cast, cast_back, cast_to_e5m6, swiglu_forward  # noqa: E402  (the reference)
+from tile_kernels.torch.cast import convert_to_e2m1_bits  # noqa: E402
+from tile_kernels.torch.cast_e5m6 import _cast_to_e5m6  # noqa: E402
+
+from tilekernels_b200.testing.generator import make_config_input  # noqa: E402
+
+FLAG_SETS = [(False, False, False), (False, True, False), (True, True, True)]  # (col_major, round_sf, ue8m0)
+
+
+def raw(t: torch.Tensor) -> np.ndarray:
+    dense = torch.empty(t.shape, dtype=t.dtype)
+    dense.copy_(t)
+    return dense.flatten().view(torch.uint8).numpy().copy()
+
+
+def meta(t: torch.Tensor) -> str:
+    return json.dumps({'dtype': str(t.dtype).replace('torch.', ''), 'shape': list(t.shape), 'stride': list(t.stride())})
+
+
+def put(store: dict, key: str, t: torch.Tensor) -> None:
+    store[key + '.bytes'] = raw(t)
+    store[key + '.meta'] = np.array(meta(t))
+
+
+def special_rows(x: torch.Tensor) -> torch.Tensor:
+    """Overwrite the first rows with corner cases: zeros, signed zeros, huge, tiny, outliers."""
+    x = x.clone()
+    big = 3.3895e38 if x.dtype == torch.bfloat16 else 3.0e38
+    x[0] = 0
+    x[1] = -0.0
+    x[2, ::2] = big
+    x[2, 1::2] = -big
+    x[3] = 1e-30
+    x[4] = x[4] * 1e-3
+    x[5, 7] = 1000.0
+    x[6] = 6.0
+    x[7] = torch.linspace(-8, 8, x.shape[1]).to(x.dtype)
+    return x
+
+
+def gen_cast() -> None:
+    store = {}
+    g = torch.Generator().manual_seed(1234)
+    inputs = {
+        'bf16_33x320': special_rows(torch.randn((33, 320), generator=g)).to(torch.bfloat16),
+        'fp32_9x192': special_rows(torch.randn((9, 192), generator=g)),
+        'bf16_130x128': torch.randn((130, 128), generator=g).to(torch.bfloat16),
+    }
+    for name, x in inputs.items():
+        put(store, f'{name}/x', x)
+        T, H = x.shape
+        for fmt in ('e4m3', 'e2m1'):
+            for bs in ((1, 32), (1, 64), (1, 128), (1, H), (128, 128), (32, 32), (128, 1)):
+                if bs == (128, 1) and fmt == 'e2m1':
+                    continue
+                for col, rnd, ue in FLAG_SETS:
+                    if bs == (128, 1) and col:
+                        continue
+                    out, sf = cast(x, fmt, bs, round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+                    key = f'{name}/{fmt}/{bs[0]}x{bs[1]}/{int(col)}{int(rnd)}{int(ue)}'
+                    put(store, key + '/out', out)
+                    put(store, key + '/sf', sf)
+                    if not col:
+                        put(store, key + '/out_pre', cast(x, fmt, bs, sf=sf))
+                        if rnd and name == 'bf16_33x320':
+                            put(store, key + '/back', cast_back((out, sf), 'fp32', bs))
+    np.savez_compressed(os.path.join(HERE, 'cast.npz'), **store)
+
+
+def gen_e5m6() -> None:
+    store = {}
+    g = torch.Generator().manual_seed(4321)
+    inputs = {
+        'bf16_33x320': special_rows(torch.randn((33, 320), generator=g)).to(torch.bfloat16),
+        'fp32_9x192': special_rows(torch.randn((9, 192), generator=g)),
+    }
+    for value, tag in ((2.0 ** -20, 'minsub'), (2.0 ** -14 * 63 / 64, 'maxsub'), (2.0 ** -14, 'minnorm')):
+        x = torch.full((5, 64), value, dtype=torch.bfloat16)
+        x[:, -1] = 65024.0
+        inputs[f'bf16_special_{tag}'] = x
+        inputs[f'fp32_special_{tag}'] = x.float().fill_(value).index_fill_(1, torch.tensor([63]), 65024.0)
+    for name, x in inputs.items():
+        put(store, f'{name}/x', x)
+        for col, rnd, ue in FLAG_SETS:
+            out, sf = cast_to_e5m6(x, x.shape[1], col, rnd, ue)
+            key = f'{name}/{int(col)}{int(rnd)}{int(ue)}'
+            put(store, key + '/out', out)
+            put(store, key + '/sf', sf)
+    # element-level known answers: codes of a sweep of floats, before packing
+    v = torch.cat([torch.randn(4096, generator=g) * s for s in (1e-6, 1e-4, 1e-2, 1.0, 100.0, 20000.0)]).clamp(-65024, 65024)
+    v = torch.cat([v, torch.tensor([0.0, -0.0, 65024.0, -65024.0, 2.0 ** -20, 2.0 ** -21, 2.0 ** -14, 1.0 + 2.0 ** -7, 1.0 + 3 * 2.0 ** -7])])
+    v = torch.cat([v, torch.zeros(8 - v.numel() % 8 if v.numel() % 8 else 0)])
+    put(store, 'kat/x', v)
+    put(store, 'kat/words', _cast_to_e5m6(v.view(1, -1)))
+    np.savez_compressed(os.path.join(HERE, 'e5m6.npz'), **store)
+
+
+def gen_e2m1_kat() -> None:
+    store = {}
+    mids = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    vals = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, 7.0, 1e9, 1e-9]
+    pts = []
+    for m in mids + vals:
+        t = torch.tensor([m], dtype=torch.float32)
+        pts += [t, torch.nextafter(t, torch.tensor([10.0])), torch.nextafter(t, torch.tensor([-10.0]))]
+    g = torch.Generator().manual_seed(99)
+    v = torch.cat(pts + [torch.randn(8192, generator=g) * 2.5])
+    v = torch.cat([v, -v])
+    put(store, 'x', v)
+    put(store, 'codes', convert_to_e2m1_bits(v, 6.0, 'cpu'))
+    np.savez_compressed(os.path.join(HERE, 'e2m1_kat.npz'), **store)
+
+
+def gen_swiglu() -> None:
+    """Reference outputs of cast(swiglu_forward(x), ...).  torch's CPU exp differs from this project's
+    exp in the last bit of a few percent of the activations, so these are compared with a tolerance."""
+    store = {}
+    g = torch.Generator().manual_seed(777)
+    T, H = 48, 256
+    x = torch.randn((T, 2 * H), generator=g).to(torch.bfloat16)
+    put(store, 'x', x)
+    pos = torch.randperm(T, generator=g).to(torch.int32)
+    pos[::7] = -1
+    w = torch.rand((8, 6), generator=g)
+    put(store, 'pos_to_token_topk', pos)
+    put(store, 'topk_weights', w)
+    for with_w in (False, True):
+        for clamp in (None, 0.5):
+            counts = torch.zeros(3, dtype=torch.int64)
+            y = swiglu_forward(x, pos if with_w else None, w if with_w else None, clamp, counts if clamp else None)
+            key0 = f'w{int(with_w)}/c{clamp}'
+            put(store, key0 + '/y', y)
+            put(store, key0 + '/counts', counts)
+            for G in (128, H):
+                for col, rnd, ue in FLAG_SETS:
+                    if G == H and col:
+                        continue
+                    out, sf = cast(y, 'e4m3', (1, G), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+                    key = f'{key0}/g{G}/{int(col)}{int(rnd)}{int(ue)}'
+                    put(store, key + '/out', out)
+                    put(store, key + '/sf', sf)
+    np.savez_compressed(os.path.join(HERE, 'swiglu.npz'), **store)
+
+
+def sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(raw(t).tobytes()).hexdigest()
+
+
+def gen_config_digests() -> None:
+    """Reference outputs of the five benchmark workloads at reduced row counts, as digests."""
+    d = {}
+
+    def add(name, x, out, sf):
+        d[name] = {'rows': x.shape[0], 'x': sha(x), 'out': sha(out), 'sf': sha(sf), 'sf_meta': json.loads(meta(sf))}
+
+    x = make_config_input('cfg1', 1280)
+    add('cfg1_per_token_e4m3_g128', x, *cast(x, 'e4m3', (1, 128)))
+    add('cfg1_per_token_e4m3_g128_round', x, *cast(x, 'e4m3', (1, 128), round_sf=True))
+    x = make_config_input('cfg2', 1024)
+    add('cfg2_per_block_128x128', x, *cast(x, 'e4m3', (128, 128)))
+    add('cfg2_per_channel_128', x, *cast(x, 'e4m3', (128, 1)))
+    x = make_config_input('cfg4', 512)
+    add('cfg4_fp4_g32_ue8m0', x, *cast(x, 'e2m1', (1, 32), round_sf=True, use_tma_aligned_col_major_sf=True, use_packed_ue8m0=True))
+    add('cfg4_e5m6', x, *cast_to_e5m6(x, x.shape[1]))
+    x = make_config_input('cfg5', 1024)
+    add('cfg5_per_token_e4m3_g128_ue8m0', x, *cast(x, 'e4m3', (1, 128), round_sf=True, use_tma_aligned_col_major_sf=True, use_packed_ue8m0=True))
+    with open(os.path.join(HERE, 'config_digests.json'), 'w') as f:
+        json.dump(d, f, indent=1, sort_keys=True)
+
+
+if __name__ == '__main__':
+    torch.set_num_threads(8)
+    gen_cast()
+    gen_e5m6()
+    gen_e2m1_kat()
+    gen_swiglu()
+    gen_config_digests()
+    for f in sorted(os.listdir(HERE)):
+        print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -1,0 +1,208 @@
+// Device-side building blocks shared by every cast kernel: wide global loads and
+// stores, bf16 unpacking, the scale arithmetic, the saturating converters and the
+// scale-factor addressing.  sm_100a only.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tkquant.h"
+
+namespace tkq {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+struct alignas(32) U32x8 {
+    uint32_t v[8];
+};
+struct alignas(16) U32x4 {
+    uint32_t v[4];
+};
+
+// ---------------------------------------------------------------------------
+// Global memory access.  Inputs are read once and outputs written once, so
+// loads bypass L1 (256-bit loads are also marked evict-first in L2, a hint PTX only
+// accepts on that width); stores do not allocate in L1.
+// sm_100 has 256-bit global loads: one instruction moves 16 bf16 per lane.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ U32x8 ldg256(const void* p) {
+    U32x8 r;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
+                   "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ U32x4 ldg128(const void* p) {
+    U32x4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.L1::no_allocate.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void stg64(void* p, uint32_t a, uint32_t b) {
+    asm volatile("st.global.L1::no_allocate.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
+__device__ __forceinline__ void stg32(void* p, uint32_t a) {
+    asm volatile("st.global.L1::no_allocate.b32 [%0], %1;" ::"l"(p), "r"(a) : "memory");
+}
+
+// A 32-bit word holds two bf16: element 2i in the low half, 2i+1 in the high half.
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// ---------------------------------------------------------------------------
+// Scale arithmetic (reference: tile_kernels/quant/common.py:196-216 get_sf_and_inv;
+// oracle form tile_kernels/torch/cast.py:147-164).
+//   sf  = max(amax, clamp) / MAX                       IEEE division
+//   inv = MAX / max(amax, clamp)                       second division, not 1/sf
+// With rounding, sf becomes the next power of two >= sf and inv its exact
+// reciprocal.  `e8` is the biased exponent byte stored in ue8m0 mode: the rounded
+// exponent, or the truncated one when rounding is off (what the oracle stores).
+// ---------------------------------------------------------------------------
+struct Scale {
+    float sf;
+    float inv;
+    uint32_t e8;
+};
+
+__device__ __forceinline__ Scale make_scale(float amax, float clamp_min, float max_q, bool round_sf) {
+    Scale s;
+    const float a = fmaxf(amax, clamp_min);
+    const float sf = __fdiv_rn(a, max_q);
+    const uint32_t bits = __float_as_uint(sf);
+    if (!round_sf) {
+        s.sf = sf;
+        s.inv = bits == 0 ? 0.0f : __fdiv_rn(max_q, a);
+        s.e8 = bits >> 23;
+        return s;
+    }
+    // ceil(log2(sf)) as a biased exponent: 2^(e-127) >= sf > 2^(e-128)
+    const uint32_t e = bits == 0 ? 0u : ((bits - 1u) >> 23) + 1u;
+    s.sf = __uint_as_float(e << 23);
+    s.inv = bits == 0 ? 0.0f : __uint_as_float((254u - e) << 23);
+    s.e8 = e;
+    return s;
+}
+
+// Where a scale goes (reference: tile_kernels/quant/common.py:238-244 store_sf).
+// m = token-block index, k = channel-block index.
+__device__ __forceinline__ void store_sf_f32(void* sf, int64_t sf_stride, bool col_major, int64_t m, int64_t k,
+                                             float v) {
+    float* p = static_cast<float*>(sf);
+    p[col_major ? k * sf_stride + m : m * sf_stride + k] = v;
+}
+
+__device__ __forceinline__ float load_sf_f32_row_major(const void* sf, int64_t sf_stride, int64_t m, int64_t k) {
+    return static_cast<const float*>(sf)[m * sf_stride + k];
+}
+
+// Packed ue8m0: one 32-bit word holds the exponent bytes of channel blocks 4*kq .. 4*kq+3
+// of token-block m; sf_stride counts bytes between consecutive kq.
+__device__ __forceinline__ void store_sf_ue8m0_word(void* sf, int64_t sf_stride, int64_t m, int64_t kq, uint32_t word) {
+    uint8_t* p = static_cast<uint8_t*>(sf) + kq * sf_stride + 4 * m;
+    *reinterpret_cast<uint32_t*>(p) = word;
+}
+
+// ---------------------------------------------------------------------------
+// Converters.  cvt.rn.satfinite rounds to nearest even and saturates to the
+// largest finite value, which equals the reference's clamp-then-convert.
+// The first source operand lands in the upper half of the result.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+    return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+// Two values -> one byte, `lo` in the low nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+    uint32_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float* v) {
+    return cvt_e2m1x2(v[0], v[1]) | (cvt_e2m1x2(v[2], v[3]) << 8) | (cvt_e2m1x2(v[4], v[5]) << 16) |
+           (cvt_e2m1x2(v[6], v[7]) << 24);
+}
+
+// fp32 -> 12-bit E5M6 code: fp16 with round-toward-zero, cut to 12 bits, then round to
+// nearest even on the 17 low bits of the fp32
+// (reference: tile_kernels/quant/per_token_cast_to_e5m6_kernel.py:44-51).
+__device__ __forceinline__ uint32_t cvt_e5m6(float v) {
+    const uint32_t h = __half_as_ushort(__float2half_rz(v));
+    uint32_t c = h >> 4;
+    const uint32_t rem = __float_as_uint(v) & 0x1FFFFu;
+    c += ((c & 1u) + rem > 0x10000u) ? 1u : 0u;
+    return c & 0xFFFu;
+}
+
+// Eight codes -> three words (per_token_cast_to_e5m6_kernel.py:53-64).
+__device__ __forceinline__ void pack_e5m6x8(const uint32_t* c, uint32_t* w) {
+    w[0] = (c[0] << 20) | (c[1] << 8) | (c[2] >> 4);
+    w[1] = (c[2] << 28) | (c[3] << 16) | (c[4] << 4) | (c[5] >> 8);
+    w[2] = (c[5] << 24) | (c[6] << 12) | c[7];
+}
+
+// ---------------------------------------------------------------------------
+// exp(x) from IEEE add/mul/fma only, so that the CPU checker (oracle/tkq_oracle.c,
+// tkq_expf) reproduces it bit for bit; CUDA's own expf goes through the
+// hardware ex2 approximation, which no CPU can reproduce.  Within 1 ulp.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float tkq_expf(float x) {
+    if (!(x < 88.72284f)) return x != x ? x : __int_as_float(0x7f800000);
+    if (x < -104.0f) return 0.0f;
+    const float shift = 12582912.0f;
+    const float jf = __fsub_rn(__fmaf_rn(x, 1.4426950408889634f, shift), shift);
+    const float rh = __fmaf_rn(jf, -0.693145751953125f, x);
+    const float rl = __fmul_rn(jf, -1.428606765330187e-06f);
+    const float r = __fadd_rn(rh, rl);
+    const float rc = __fadd_rn(__fsub_rn(rh, r), rl);
+    float q = 2.4801587301587302e-05f;
+    q = __fmaf_rn(q, r, 1.9841269841269841e-04f);
+    q = __fmaf_rn(q, r, 1.3888888888888889e-03f);
+    q = __fmaf_rn(q, r, 8.3333333333333332e-03f);
+    q = __fmaf_rn(q, r, 4.1666666666666664e-02f);
+    q = __fmaf_rn(q, r, 1.6666666666666666e-01f);
+    q = __fmaf_rn(q, r, 0.5f);
+    const float wl = __fmul_rn(__fmul_rn(r, r), q);
+    const float s = __fadd_rn(1.0f, r);
+    const float e = __fadd_rn(__fsub_rn(1.0f, s), r);
+    float p = __fadd_rn(s, __fadd_rn(__fadd_rn(e, rc), wl));
+    const int j = static_cast<int>(jf);
+    const int j1 = j / 2, j2 = j - j1;
+    p = __fmul_rn(p, __uint_as_float(static_cast<uint32_t>(j1 + 127) << 23));
+    return __fmul_rn(p, __uint_as_float(static_cast<uint32_t>(j2 + 127) << 23));
+}
+
+// silu(g) * u evaluated as (g / (1 + exp(-g))) * u with IEEE division
+// (reference: tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:140-144).
+__device__ __forceinline__ float swiglu(float g, float u) {
+    const float d = __fadd_rn(1.0f, tkq_expf(-g));
+    return __fmul_rn(__fdiv_rn(g, d), u);
+}
+
+// ---------------------------------------------------------------------------
+// Host-side helpers
+// ---------------------------------------------------------------------------
+int set_error(int code, const char* msg);          // records msg for tkq_last_error_string, returns code
+int check_launch(const char* what);                 // cudaGetLastError -> return code
+int device_sm_count();                              // cached per device
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace tkq

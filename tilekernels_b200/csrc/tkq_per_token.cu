@@ -1,0 +1,183 @@
+// C entry points of the per-token casts (FP8 e4m3, FP4 e2m1, E5M6).
+#include <algorithm>
+
+#include "tkq_launch.cuh"
+#include "tkq_token_kernels.cuh"
+
+namespace tkq {
+
+template <int DT, int FMT, int LPG>
+static int launch_group(const TokenCastParams& p, cudaStream_t stream) {
+    constexpr int U = DT == TKQ_DT_BF16 ? 4 : 2;
+    auto kernel = group_cast_kernel<PlainSource<DT>, false, FMT, LPG, U, 0>;
+    const int64_t warps_needed = (static_cast<int64_t>(p.total_items) + U - 1) / U;
+    const int grid = grid_size(kernel, kGroupThreads, (warps_needed + kGroupThreads / 32 - 1) / (kGroupThreads / 32), 0);
+    kernel<<<grid, kGroupThreads, 0, stream>>>(p);
+    return check_launch("per_token_cast (group kernel)");
+}
+
+template <int DT, int FMT>
+static int dispatch_group(const TokenCastParams& p, int64_t g, cudaStream_t stream) {
+    switch (g) {
+        case 16: return launch_group<DT, FMT, 1>(p, stream);
+        case 32: return launch_group<DT, FMT, 2>(p, stream);
+        case 64: return launch_group<DT, FMT, 4>(p, stream);
+        case 128: return launch_group<DT, FMT, 8>(p, stream);
+    }
+    return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: num_per_channels must be 16, 32, 64, 128 or hidden");
+}
+
+template <int DT, int FMT, int K>
+static int launch_row(const TokenCastParams& p, int threads, cudaStream_t stream) {
+    auto kernel = row_cast_kernel<PlainSource<DT>, false, FMT, K, 0>;
+    const int grid = grid_size(kernel, threads, p.num_tokens, 0);
+    kernel<<<grid, threads, 0, stream>>>(p);
+    return check_launch("per_token_cast (row kernel)");
+}
+
+template <int DT, int FMT>
+static int dispatch_row(const TokenCastParams& p, cudaStream_t stream) {
+    int k = 0, threads = 0;
+    if (!row_shape(p.hidden / 16, kRowMaxThreads, &k, &threads))
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: hidden too large for one scale per token (max 32768)");
+    switch (k) {
+        case 1: return launch_row<DT, FMT, 1>(p, threads, stream);
+        case 2: return launch_row<DT, FMT, 2>(p, threads, stream);
+        default: return launch_row<DT, FMT, 4>(p, threads, stream);
+    }
+}
+
+template <int DT, int K>
+static int launch_e5m6(const TokenCastParams& p, int threads, cudaStream_t stream) {
+    auto kernel = row_cast_e5m6_kernel<DT, K>;
+    const int grid = grid_size(kernel, threads, p.num_tokens, 0);
+    kernel<<<grid, threads, 0, stream>>>(p);
+    return check_launch("per_token_cast_e5m6");
+}
+
+template <int DT>
+static int dispatch_e5m6(const TokenCastParams& p, cudaStream_t stream) {
+    int k = 0, threads = 0;
+    if (!row_shape((p.hidden + 31) / 32, kRowMaxThreads, &k, &threads))
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast_e5m6: hidden too large (max 65536)");
+    switch (k) {
+        case 1: return launch_e5m6<DT, 1>(p, threads, stream);
+        case 2: return launch_e5m6<DT, 2>(p, threads, stream);
+        default: return launch_e5m6<DT, 4>(p, threads, stream);
+    }
+}
+
+static int check_sf_flags(unsigned flags, const void* sf, int64_t sf_stride, const char** why) {
+    if ((flags & TKQ_SF_UE8M0) && !(flags & TKQ_SF_COL_MAJOR)) {
+        *why = "packed ue8m0 scales need the column-major layout";
+        return TKQ_E_UNSUPPORTED;
+    }
+    if ((flags & TKQ_CAST_ONLY) && (flags & (TKQ_SF_UE8M0 | TKQ_SF_COL_MAJOR | TKQ_SF_ONLY))) {
+        *why = "precomputed scales must be row-major fp32";
+        return TKQ_E_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(sf) & 3u) || ((flags & TKQ_SF_UE8M0) && (sf_stride & 3))) {
+        *why = "scale storage must be 4-byte aligned";
+        return TKQ_E_ALIGNMENT;
+    }
+    return 0;
+}
+
+}  // namespace tkq
+
+using namespace tkq;
+
+extern "C" int tkq_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int64_t x_row_stride,
+                                  int fmt, int64_t num_per_channels, unsigned flags, void* out, void* sf,
+                                  int64_t sf_stride, void* stream) {
+    if (fmt == TKQ_FMT_E5M6) {
+        if (num_per_channels != hidden)
+            return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: e5m6 needs num_per_channels == hidden");
+        return tkq_per_token_cast_e5m6(x, in_dtype, num_tokens, hidden, x_row_stride, flags, out, sf, sf_stride, stream);
+    }
+    if (num_tokens < 0 || hidden <= 0 || x_row_stride < hidden || num_per_channels <= 0 ||
+        (in_dtype != TKQ_DT_BF16 && in_dtype != TKQ_DT_FP32) || (fmt != TKQ_FMT_E4M3 && fmt != TKQ_FMT_E2M1))
+        return set_error(TKQ_E_BAD_ARG, "per_token_cast: bad size, dtype or format");
+    if (num_tokens == 0) return 0;
+    const bool sf_only = flags & TKQ_SF_ONLY;
+    if (x == nullptr || sf == nullptr || (!sf_only && out == nullptr))
+        return set_error(TKQ_E_BAD_ARG, "per_token_cast: null pointer");
+    const char* why = "";
+    if (int rc = check_sf_flags(flags, sf, sf_stride, &why)) return set_error(rc, why);
+    const int elem = in_dtype == TKQ_DT_BF16 ? 2 : 4;
+    if (hidden % 16 != 0) return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: hidden must be a multiple of 16");
+    if (!aligned16(x) || (x_row_stride * elem) % 16 != 0 || (!sf_only && !aligned16(out)))
+        return set_error(TKQ_E_ALIGNMENT, "per_token_cast: x and out must be 16-byte aligned, rows too");
+
+    TokenCastParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = sf;
+    p.x_stride = x_row_stride;
+    p.sf_stride = sf_stride;
+    p.out_stride = fmt == TKQ_FMT_E4M3 ? hidden : hidden / 2;
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.flags = flags;
+    p.clamp_min = fmt == TKQ_FMT_E4M3 ? 1e-4f : 6.0f * 1.1754943508222875e-38f;  // 6 * 2^-126
+    p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((x_row_stride * elem) % 32 == 0);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    const bool group_kernel = num_per_channels == 16 || num_per_channels == 32 || num_per_channels == 64 ||
+                              num_per_channels == 128;
+    if (group_kernel) {
+        const int64_t steps = (hidden + 511) / 512;
+        if (num_tokens * steps >= (int64_t{1} << 31))
+            return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: more than 2^31 work items; split the token dimension");
+        p.steps_per_row = static_cast<uint32_t>(steps);
+        p.num_groups = static_cast<uint32_t>((hidden + num_per_channels - 1) / num_per_channels);
+        p.total_items = static_cast<uint32_t>(num_tokens * steps);
+        if (in_dtype == TKQ_DT_BF16)
+            return fmt == TKQ_FMT_E4M3 ? dispatch_group<TKQ_DT_BF16, TKQ_FMT_E4M3>(p, num_per_channels, s)
+                                       : dispatch_group<TKQ_DT_BF16, TKQ_FMT_E2M1>(p, num_per_channels, s);
+        return fmt == TKQ_FMT_E4M3 ? dispatch_group<TKQ_DT_FP32, TKQ_FMT_E4M3>(p, num_per_channels, s)
+                                   : dispatch_group<TKQ_DT_FP32, TKQ_FMT_E2M1>(p, num_per_channels, s);
+    }
+    if (num_per_channels != hidden)
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: num_per_channels must be 16, 32, 64, 128 or hidden");
+    if (flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY))
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: sf-only / cast-only need num_per_channels < hidden");
+    p.num_groups = 1;
+    if (in_dtype == TKQ_DT_BF16)
+        return fmt == TKQ_FMT_E4M3 ? dispatch_row<TKQ_DT_BF16, TKQ_FMT_E4M3>(p, s)
+                                   : dispatch_row<TKQ_DT_BF16, TKQ_FMT_E2M1>(p, s);
+    return fmt == TKQ_FMT_E4M3 ? dispatch_row<TKQ_DT_FP32, TKQ_FMT_E4M3>(p, s) : dispatch_row<TKQ_DT_FP32, TKQ_FMT_E2M1>(p, s);
+}
+
+extern "C" int tkq_per_token_cast_e5m6(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden,
+                                       int64_t x_row_stride, unsigned flags, void* out, void* sf, int64_t sf_stride,
+                                       void* stream) {
+    if (num_tokens < 0 || hidden <= 0 || x_row_stride < hidden || (in_dtype != TKQ_DT_BF16 && in_dtype != TKQ_DT_FP32))
+        return set_error(TKQ_E_BAD_ARG, "per_token_cast_e5m6: bad size or dtype");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || sf == nullptr || out == nullptr) return set_error(TKQ_E_BAD_ARG, "per_token_cast_e5m6: null pointer");
+    if (flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY))
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast_e5m6: sf-only / cast-only are not defined for e5m6");
+    const char* why = "";
+    if (int rc = check_sf_flags(flags, sf, sf_stride, &why)) return set_error(rc, why);
+    if (hidden % 8 != 0) return set_error(TKQ_E_UNSUPPORTED, "per_token_cast_e5m6: hidden must be a multiple of 8");
+    const int elem = in_dtype == TKQ_DT_BF16 ? 2 : 4;
+    if (!aligned16(x) || (x_row_stride * elem) % 16 != 0 || !aligned16(out))
+        return set_error(TKQ_E_ALIGNMENT, "per_token_cast_e5m6: x and out must be 16-byte aligned, rows too");
+
+    TokenCastParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = sf;
+    p.x_stride = x_row_stride;
+    p.sf_stride = sf_stride;
+    p.out_stride = hidden / 8 * 12;
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.num_groups = 1;
+    p.flags = flags;
+    p.clamp_min = 1e-4f;
+    p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((x_row_stride * elem) % 32 == 0);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return in_dtype == TKQ_DT_BF16 ? dispatch_e5m6<TKQ_DT_BF16>(p, s) : dispatch_e5m6<TKQ_DT_FP32>(p, s);
+}

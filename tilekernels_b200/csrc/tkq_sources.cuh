@@ -1,0 +1,162 @@
+// "Sources": how a lane obtains the 16 consecutive fp32 values it owns.
+//
+// A source has a Raw type (the registers of the global loads, kept untouched so
+// that several loads stay in flight), issue() that starts the loads, and
+// unpack() that turns Raw into 16 floats.  Two families exist:
+//   PlainSource<DT>   the input tensor itself (bf16 or fp32)
+//   SwigluSource<DT>  silu(gate) * up (* row weight), gate at column c and up at
+//                     column c + hidden of a [tokens, 2 * hidden] tensor
+// 256-bit loads need 32-byte aligned addresses; `wide = false` falls back to pairs
+// of 128-bit loads for tensors that are only 16-byte aligned.
+#pragma once
+
+#include "tkq_common.cuh"
+
+namespace tkq {
+
+template <int DT>
+struct PlainSource;
+
+template <>
+struct PlainSource<TKQ_DT_BF16> {
+    static constexpr int kElemBytes = 2;
+    struct Raw {
+        U32x8 a;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.a.v[i] = 0;
+    }
+    // p points at the lane's first element; `wide` = p is 32-byte aligned
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool wide) {
+        if (wide) {
+            r.a = ldg256(p);
+        } else {
+            const U32x4 lo = ldg128(p), hi = ldg128(static_cast<const uint8_t*>(p) + 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                r.a.v[i] = lo.v[i];
+                r.a.v[4 + i] = hi.v[i];
+            }
+        }
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = bf16_lo(r.a.v[i]);
+            v[2 * i + 1] = bf16_hi(r.a.v[i]);
+        }
+    }
+};
+
+template <>
+struct PlainSource<TKQ_DT_FP32> {
+    static constexpr int kElemBytes = 4;
+    struct Raw {
+        U32x8 a, b;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.a.v[i] = r.b.v[i] = 0;
+    }
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool wide) {
+        if (wide) {
+            r.a = ldg256(p);
+            r.b = ldg256(static_cast<const uint8_t*>(p) + 32);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const U32x4 a = ldg128(static_cast<const uint8_t*>(p) + 16 * h);
+                const U32x4 b = ldg128(static_cast<const uint8_t*>(p) + 32 + 16 * h);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    r.a.v[4 * h + i] = a.v[i];
+                    r.b.v[4 * h + i] = b.v[i];
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = __uint_as_float(r.a.v[i]);
+            v[8 + i] = __uint_as_float(r.b.v[i]);
+        }
+    }
+};
+
+// Clamp bookkeeping of the SwiGLU source: per-thread counters of clamped inputs.
+struct ClampCounters {
+    uint32_t gate_hi = 0, up_hi = 0, up_lo = 0;
+};
+
+template <int DT>
+struct SwigluSource {
+    using P = PlainSource<DT>;
+    static constexpr int kElemBytes = P::kElemBytes;
+    struct Raw {
+        typename P::Raw g, u;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) {
+        P::zero(r.g);
+        P::zero(r.u);
+    }
+    // p points at the lane's first gate element; the up half is `hidden` elements further
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool wide, int64_t hidden) {
+        P::issue(r.g, p, wide);
+        P::issue(r.u, static_cast<const uint8_t*>(p) + hidden * kElemBytes, wide);
+    }
+    // kClamp: apply the clamp; kCount: also count what was clamped; kWeight: multiply by w
+    template <bool kClamp, bool kCount, bool kWeight>
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v, float clamp, float w, ClampCounters& cnt) {
+        float g[16], u[16];
+        P::unpack(r.g, g);
+        P::unpack(r.u, u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float gi = g[i], ui = u[i];
+            if (kClamp) {
+                if (kCount) {
+                    cnt.gate_hi += gi > clamp;
+                    cnt.up_hi += ui > clamp;
+                    cnt.up_lo += ui < -clamp;
+                }
+                gi = gi > clamp ? clamp : gi;
+                ui = ui > clamp ? clamp : ui;
+                ui = ui < -clamp ? -clamp : ui;
+            }
+            float y = swiglu(gi, ui);
+            if (kWeight) y = __fmul_rn(y, w);
+            v[i] = y;
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// The common tail of every cast: 16 scaled values of one lane -> packed codes.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float absmax16(const float* v) {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+}
+
+// e4m3: 16 bytes at out_row + col
+__device__ __forceinline__ void quantize_store_e4m3x16(const float* v, float inv, uint8_t* dst) {
+    float s[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], inv);
+    stg128(dst, cvt_e4m3x4(s[0], s[1], s[2], s[3]), cvt_e4m3x4(s[4], s[5], s[6], s[7]),
+           cvt_e4m3x4(s[8], s[9], s[10], s[11]), cvt_e4m3x4(s[12], s[13], s[14], s[15]));
+}
+
+// e2m1: 8 bytes at out_row + col / 2
+__device__ __forceinline__ void quantize_store_e2m1x16(const float* v, float inv, uint8_t* dst) {
+    float s[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], inv);
+    stg64(dst, cvt_e2m1x8(s), cvt_e2m1x8(s + 8));
+}
+
+}  // namespace tkq

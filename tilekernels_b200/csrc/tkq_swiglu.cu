@@ -1,0 +1,100 @@
+// C entry point of the fused SwiGLU + per-token e4m3 cast.
+#include "tkq_launch.cuh"
+#include "tkq_token_kernels.cuh"
+
+namespace tkq {
+
+template <int DT, int kClampMode>
+static int launch_swiglu_group(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
+    constexpr int U = DT == TKQ_DT_BF16 ? 2 : 1;  // two input streams per item
+    auto kernel = group_cast_kernel<SwigluSource<DT>, true, TKQ_FMT_E4M3, 8, U, kClampMode>;
+    const int64_t warps_needed = (static_cast<int64_t>(p.total_items) + U - 1) / U;
+    const int grid = grid_size(kernel, kGroupThreads, (warps_needed + kGroupThreads / 32 - 1) / (kGroupThreads / 32), 0,
+                               sm_limit);
+    kernel<<<grid, kGroupThreads, 0, stream>>>(p);
+    return check_launch("swiglu_forward_and_per_token_cast (group kernel)");
+}
+
+template <int DT, int kClampMode, int K>
+static int launch_swiglu_row(const TokenCastParams& p, int threads, int sm_limit, cudaStream_t stream) {
+    auto kernel = row_cast_kernel<SwigluSource<DT>, true, TKQ_FMT_E4M3, K, kClampMode>;
+    const int grid = grid_size(kernel, threads, p.num_tokens, 0, sm_limit);
+    kernel<<<grid, threads, 0, stream>>>(p);
+    return check_launch("swiglu_forward_and_per_token_cast (row kernel)");
+}
+
+template <int DT, int kClampMode>
+static int dispatch_swiglu(const TokenCastParams& p, bool per_row_scale, int sm_limit, cudaStream_t stream) {
+    if (!per_row_scale) return launch_swiglu_group<DT, kClampMode>(p, sm_limit, stream);
+    int k = 0, threads = 0;
+    // K is capped at 2: the activations stay in registers as fp32 between the maximum and the conversion
+    if (!row_shape(p.hidden / 16, kRowMaxThreads, &k, &threads) || k > 2)
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: hidden too large for one scale per token (max 16384)");
+    return k == 1 ? launch_swiglu_row<DT, kClampMode, 1>(p, threads, sm_limit, stream)
+                  : launch_swiglu_row<DT, kClampMode, 2>(p, threads, sm_limit, stream);
+}
+
+template <int DT>
+static int dispatch_clamp(const TokenCastParams& p, bool per_row_scale, int sm_limit, cudaStream_t stream) {
+    if (p.swiglu_clamp < 0.0f) return dispatch_swiglu<DT, 0>(p, per_row_scale, sm_limit, stream);
+    if (p.clamped_count == nullptr) return dispatch_swiglu<DT, 1>(p, per_row_scale, sm_limit, stream);
+    return dispatch_swiglu<DT, 2>(p, per_row_scale, sm_limit, stream);
+}
+
+}  // namespace tkq
+
+using namespace tkq;
+
+extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden,
+                                                     int64_t num_per_channels, const int32_t* pos_to_token_topk,
+                                                     const float* topk_weights, const int32_t* pos_to_expert,
+                                                     float swiglu_clamp, long long* clamped_count, float sf_clamp_min,
+                                                     int num_sms, unsigned flags, void* out, void* sf, int64_t sf_stride,
+                                                     void* stream) {
+    if (num_tokens < 0 || hidden <= 0 || (in_dtype != TKQ_DT_BF16 && in_dtype != TKQ_DT_FP32))
+        return set_error(TKQ_E_BAD_ARG, "swiglu cast: bad size or dtype");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || out == nullptr || sf == nullptr) return set_error(TKQ_E_BAD_ARG, "swiglu cast: null pointer");
+    if ((pos_to_token_topk == nullptr) != (topk_weights == nullptr))
+        return set_error(TKQ_E_BAD_ARG, "swiglu cast: pos_to_token_topk and topk_weights go together");
+    if (clamped_count != nullptr && swiglu_clamp < 0.0f)
+        return set_error(TKQ_E_BAD_ARG, "swiglu cast: clamped_count needs a clamp value");
+    if (flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY)) return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: sf-only / cast-only not defined");
+    if ((flags & TKQ_SF_UE8M0) && !(flags & TKQ_SF_COL_MAJOR))
+        return set_error(TKQ_E_UNSUPPORTED, "packed ue8m0 scales need the column-major layout");
+    if (hidden % 128 != 0) return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: hidden must be a multiple of 128");
+    const bool per_row_scale = num_per_channels != 128;
+    if (per_row_scale && num_per_channels != hidden)
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: num_per_channels must be 128 or hidden");
+    const int elem = in_dtype == TKQ_DT_BF16 ? 2 : 4;
+    if (!aligned16(x) || !aligned16(out) || (reinterpret_cast<uintptr_t>(sf) & 3u) || ((flags & TKQ_SF_UE8M0) && (sf_stride & 3)))
+        return set_error(TKQ_E_ALIGNMENT, "swiglu cast: x and out must be 16-byte aligned, sf 4-byte aligned");
+
+    TokenCastParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = sf;
+    p.x_stride = 2 * hidden;
+    p.sf_stride = sf_stride;
+    p.out_stride = hidden;
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.flags = flags;
+    p.clamp_min = sf_clamp_min < 0.0f ? 1e-4f : sf_clamp_min;
+    p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((hidden * elem) % 32 == 0);
+    p.pos_to_token_topk = pos_to_token_topk;
+    p.topk_weights = topk_weights;
+    p.pos_to_expert = pos_to_expert;
+    p.swiglu_clamp = swiglu_clamp;
+    p.clamped_count = reinterpret_cast<unsigned long long*>(clamped_count);
+    const int64_t steps = (hidden + 511) / 512;
+    if (num_tokens * steps >= (int64_t{1} << 31))
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: more than 2^31 work items; split the token dimension");
+    p.steps_per_row = static_cast<uint32_t>(steps);
+    p.num_groups = per_row_scale ? 1u : static_cast<uint32_t>(hidden / 128);
+    p.total_items = static_cast<uint32_t>(num_tokens * steps);
+    const int sm_limit = clamped_count != nullptr ? num_sms : 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return in_dtype == TKQ_DT_BF16 ? dispatch_clamp<TKQ_DT_BF16>(p, per_row_scale, sm_limit, s)
+                                   : dispatch_clamp<TKQ_DT_FP32>(p, per_row_scale, sm_limit, s);
+}

@@ -1,0 +1,362 @@
+// Row-wise ("per-token") cast kernels.
+//
+// Work decomposition.  Every lane owns 16 consecutive values of one row, so a
+// warp covers a 512-value span ("step") of a row per item:
+//   * bf16 input: one 256-bit load per lane, 1 KB contiguous per warp
+//   * e4m3 output: one 128-bit store per lane, 512 B contiguous per warp
+//   * a 128-wide scale group is 8 adjacent lanes, reduced with 3 shuffles, and the
+//     4 groups of a step are exactly one packed ue8m0 word
+// group_cast_kernel handles scale groups of 16..128 values (LPG = lanes per group);
+// row_cast_kernel handles one scale per row, reduced across the thread block.
+#pragma once
+
+#include "tkq_sources.cuh"
+
+namespace tkq {
+
+struct TokenCastParams {
+    const void* x;
+    uint8_t* out;
+    void* sf;
+    int64_t x_stride;    // elements between rows of x
+    int64_t sf_stride;   // see tkquant.h
+    int64_t out_stride;  // bytes between rows of out
+    int64_t num_tokens;
+    int64_t hidden;        // values per row that are quantized (SwiGLU: half the input columns)
+    uint32_t steps_per_row;  // ceil(hidden / 512)
+    uint32_t num_groups;     // scale groups per row
+    uint32_t total_items;    // num_tokens * steps_per_row
+    uint32_t flags;
+    float clamp_min;
+    bool wide_loads;  // every row of x starts on a 32-byte boundary: 256-bit loads are legal
+    // SwiGLU only
+    const int32_t* pos_to_token_topk;
+    const float* topk_weights;
+    const int32_t* pos_to_expert;
+    float swiglu_clamp;
+    unsigned long long* clamped_count;
+};
+
+constexpr int kGroupThreads = 256;
+
+template <int FMT>
+struct FmtTraits;
+template <>
+struct FmtTraits<TKQ_FMT_E4M3> {
+    static constexpr float kMax = 448.0f;
+};
+template <>
+struct FmtTraits<TKQ_FMT_E2M1> {
+    static constexpr float kMax = 6.0f;
+};
+
+__device__ __forceinline__ void flush_clamp_counters(const ClampCounters& cnt, unsigned long long* dst) {
+    uint32_t a = cnt.gate_hi, b = cnt.up_hi, c = cnt.up_lo;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(kFullMask, a, o);
+        b += __shfl_xor_sync(kFullMask, b, o);
+        c += __shfl_xor_sync(kFullMask, c, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (a) atomicAdd(dst + 0, static_cast<unsigned long long>(a));
+        if (b) atomicAdd(dst + 1, static_cast<unsigned long long>(b));
+        if (c) atomicAdd(dst + 2, static_cast<unsigned long long>(c));
+    }
+}
+
+// kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count (SwiGLU sources only)
+template <class Src, bool kSwiglu, int FMT, int LPG, int U, int kClampMode>
+__global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCastParams p) {
+    constexpr float kMaxQ = FmtTraits<FMT>::kMax;
+    constexpr int kLanesPerWord = 4 * LPG;  // lanes that share one packed ue8m0 word (may exceed 32: LPG = 8 -> 32)
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    const bool col_major = p.flags & TKQ_SF_COL_MAJOR;
+    const bool ue8m0 = p.flags & TKQ_SF_UE8M0;
+    const bool sf_only = p.flags & TKQ_SF_ONLY;
+    const bool cast_only = p.flags & TKQ_CAST_ONLY;
+    const bool wide = p.wide_loads;
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    ClampCounters cnt;
+
+    for (uint32_t base = warp; base < p.total_items; base += nwarps * U) {
+        typename Src::Raw raw[U];
+        uint32_t row[U], col[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t item = base + u * nwarps;
+            live[u] = item < p.total_items;
+            row[u] = 0;
+            col[u] = 0;
+            if (live[u]) {
+                row[u] = item / p.steps_per_row;
+                col[u] = (item - row[u] * p.steps_per_row) * 512u + lane * 16u;
+                if (kSwiglu && p.pos_to_expert != nullptr && p.pos_to_expert[row[u]] < 0) live[u] = false;
+            }
+            if (live[u] && col[u] < p.hidden) {
+                const uint8_t* src = xb + (static_cast<int64_t>(row[u]) * p.x_stride + col[u]) * Src::kElemBytes;
+                if constexpr (kSwiglu) Src::issue(raw[u], src, wide, p.hidden);
+                else Src::issue(raw[u], src, wide);
+            } else {
+                Src::zero(raw[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!live[u]) continue;  // warp-uniform
+            float v[16];
+            if constexpr (kSwiglu) {
+                float w = 1.0f;
+                if (p.pos_to_token_topk != nullptr) {
+                    const int32_t pos = p.pos_to_token_topk[row[u]];
+                    w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
+                }
+                Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt);
+            } else {
+                Src::unpack(raw[u], v);
+            }
+            const bool in_row = col[u] < p.hidden;
+            const uint32_t g = col[u] / (16u * LPG);
+            float inv;
+            if (cast_only) {
+                inv = in_row ? __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, row[u], g)) : 0.0f;
+            } else {
+                float amax = absmax16(v);
+#pragma unroll
+                for (int o = LPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, o));
+                const Scale s = make_scale(amax, p.clamp_min, kMaxQ, round_sf);
+                inv = s.inv;
+                if (ue8m0) {
+                    uint32_t word = 0;
+                    const uint32_t g0 = g & ~3u;
+                    const uint32_t lane0 = kLanesPerWord >= 32 ? 0u : (lane & ~static_cast<uint32_t>(kLanesPerWord - 1));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t b = __shfl_sync(kFullMask, s.e8, lane0 + k * LPG);
+                        if (g0 + k < p.num_groups) word |= b << (8 * k);
+                    }
+                    if (lane == lane0 && g < p.num_groups) store_sf_ue8m0_word(p.sf, p.sf_stride, row[u], g >> 2, word);
+                } else if (lane % LPG == 0 && in_row) {
+                    store_sf_f32(p.sf, p.sf_stride, col_major, row[u], g, s.sf);
+                }
+            }
+            if (!sf_only && in_row) {
+                if constexpr (FMT == TKQ_FMT_E4M3)
+                    quantize_store_e4m3x16(v, inv, p.out + static_cast<int64_t>(row[u]) * p.out_stride + col[u]);
+                else
+                    quantize_store_e2m1x16(v, inv, p.out + static_cast<int64_t>(row[u]) * p.out_stride + col[u] / 2);
+            }
+        }
+    }
+    if constexpr (kSwiglu && kClampMode > 1) flush_clamp_counters(cnt, p.clamped_count);
+}
+
+// ---------------------------------------------------------------------------
+// One scale per row.  A thread block walks rows; each thread keeps K chunks of 16
+// values in registers (chunk c = tid + k * blockDim.x), the block reduces the
+// maximum through shared memory with a single barrier per row.
+// ---------------------------------------------------------------------------
+constexpr int kRowMaxThreads = 512;
+
+__device__ __forceinline__ float block_max(float m, float (*red)[32], int parity) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
+    if (lane == 0) red[parity][warp] = m;
+    __syncthreads();
+    m = red[parity][lane < nw ? lane : 0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
+    return m;
+}
+
+// Stores the single scale of a row in whichever layout was asked for.
+__device__ __forceinline__ void store_row_scale(const TokenCastParams& p, int64_t row, const Scale& s) {
+    if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_word(p.sf, p.sf_stride, row, 0, s.e8);  // upper three bytes zero
+    else store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, row, 0, s.sf);
+}
+
+template <class Src, bool kSwiglu, int FMT, int K, int kClampMode>
+__global__ void __launch_bounds__(kRowMaxThreads) row_cast_kernel(const TokenCastParams p) {
+    constexpr float kMaxQ = FmtTraits<FMT>::kMax;
+    __shared__ float red[2][32];
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    const bool wide = p.wide_loads;
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    ClampCounters cnt;
+    int parity = 0;
+    for (int64_t row = blockIdx.x; row < p.num_tokens; row += gridDim.x) {
+        if (kSwiglu && p.pos_to_expert != nullptr && p.pos_to_expert[row] < 0) continue;  // block-uniform
+        typename Src::Raw raw[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int64_t col = (static_cast<int64_t>(threadIdx.x) + k * blockDim.x) * 16;
+            if (col < p.hidden) {
+                const uint8_t* src = xb + (row * p.x_stride + col) * Src::kElemBytes;
+                if constexpr (kSwiglu) Src::issue(raw[k], src, wide, p.hidden);
+                else Src::issue(raw[k], src, wide);
+            } else {
+                Src::zero(raw[k]);
+            }
+        }
+        float v[K][16];
+        float amax = 0.0f;
+        float w = 1.0f;
+        if constexpr (kSwiglu) {
+            if (p.pos_to_token_topk != nullptr) {
+                const int32_t pos = p.pos_to_token_topk[row];
+                w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            if constexpr (kSwiglu)
+                Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[k], v[k], p.swiglu_clamp, w, cnt);
+            else
+                Src::unpack(raw[k], v[k]);
+            amax = fmaxf(amax, absmax16(v[k]));
+        }
+        amax = block_max(amax, red, parity);
+        parity ^= 1;
+        const Scale s = make_scale(amax, p.clamp_min, kMaxQ, round_sf);
+        if (threadIdx.x == 0) store_row_scale(p, row, s);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int64_t col = (static_cast<int64_t>(threadIdx.x) + k * blockDim.x) * 16;
+            if (col < p.hidden) {
+                if constexpr (FMT == TKQ_FMT_E4M3) quantize_store_e4m3x16(v[k], s.inv, p.out + row * p.out_stride + col);
+                else quantize_store_e2m1x16(v[k], s.inv, p.out + row * p.out_stride + col / 2);
+            }
+        }
+    }
+    if constexpr (kSwiglu && kClampMode > 1) flush_clamp_counters(cnt, p.clamped_count);
+}
+
+// ---------------------------------------------------------------------------
+// E5M6: one scale per row (maximum 65024), 12-bit codes, 8 codes in 3 words.
+// A thread owns K chunks of 32 values = 4 octets = 12 output words = three 128-bit
+// stores.  Rows whose length is not a multiple of 32 finish with per-octet stores.
+// ---------------------------------------------------------------------------
+template <int DT>
+struct OctetLoader;
+template <>
+struct OctetLoader<TKQ_DT_BF16> {
+    static constexpr int kElemBytes = 2;
+    struct Raw {
+        U32x4 a;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) { r.a.v[0] = r.a.v[1] = r.a.v[2] = r.a.v[3] = 0; }
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool) { r.a = ldg128(p); }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = bf16_lo(r.a.v[i]);
+            v[2 * i + 1] = bf16_hi(r.a.v[i]);
+        }
+    }
+};
+template <>
+struct OctetLoader<TKQ_DT_FP32> {
+    static constexpr int kElemBytes = 4;
+    struct Raw {
+        U32x8 a;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.a.v[i] = 0;
+    }
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool wide) {
+        if (wide) {
+            r.a = ldg256(p);
+        } else {
+            const U32x4 lo = ldg128(p), hi = ldg128(static_cast<const uint8_t*>(p) + 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                r.a.v[i] = lo.v[i];
+                r.a.v[4 + i] = hi.v[i];
+            }
+        }
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r.a.v[i]);
+    }
+};
+
+template <int DT, int K>
+__global__ void __launch_bounds__(kRowMaxThreads) row_cast_e5m6_kernel(const TokenCastParams p) {
+    using L = OctetLoader<DT>;
+    __shared__ float red[2][32];
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    const bool wide = p.wide_loads;
+    const bool wide_stores = (p.hidden % 32) == 0;  // then every chunk starts on a 16-byte boundary of the output row
+    int parity = 0;
+    for (int64_t row = blockIdx.x; row < p.num_tokens; row += gridDim.x) {
+        typename L::Raw raw[K][4];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                const int64_t col = (static_cast<int64_t>(threadIdx.x) + k * blockDim.x) * 32 + o * 8;
+                if (col < p.hidden) L::issue(raw[k][o], xb + (row * p.x_stride + col) * L::kElemBytes, wide);
+                else L::zero(raw[k][o]);
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                float v[8];
+                L::unpack(raw[k][o], v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            }
+        }
+        amax = block_max(amax, red, parity);
+        parity ^= 1;
+        const Scale s = make_scale(amax, p.clamp_min, 65024.0f, round_sf);
+        if (threadIdx.x == 0) store_row_scale(p, row, s);
+        uint32_t* out_row = reinterpret_cast<uint32_t*>(p.out + row * p.out_stride);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int64_t chunk = static_cast<int64_t>(threadIdx.x) + k * blockDim.x;
+            uint32_t w[12];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+                float v[8];
+                uint32_t c[8];
+                L::unpack(raw[k][o], v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) c[i] = cvt_e5m6(__fmul_rn(v[i], s.inv));
+                pack_e5m6x8(c, w + 3 * o);
+            }
+            const int64_t col = chunk * 32;
+            if (wide_stores) {
+                if (col < p.hidden) {
+                    uint32_t* dst = out_row + chunk * 12;
+                    stg128(dst, w[0], w[1], w[2], w[3]);
+                    stg128(dst + 4, w[4], w[5], w[6], w[7]);
+                    stg128(dst + 8, w[8], w[9], w[10], w[11]);
+                }
+            } else {
+#pragma unroll
+                for (int o = 0; o < 4; ++o) {
+                    if (col + o * 8 < p.hidden) {
+                        uint32_t* dst = out_row + chunk * 12 + o * 3;
+                        stg32(dst, w[3 * o]);
+                        stg32(dst + 1, w[3 * o + 1]);
+                        stg32(dst + 2, w[3 * o + 2]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace tkq
