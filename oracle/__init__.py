@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from .build import LIB, build
+from .build import LIB, build as build_library
 
 _lib = None
 
@@ -23,7 +23,7 @@ def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         if not os.path.exists(LIB):
-            build()
+            build_library()
         _lib = ctypes.CDLL(LIB)
         _lib.tkq_expf.restype = ctypes.c_float
         _lib.tkq_expf.argtypes = [ctypes.c_float]

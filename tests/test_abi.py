@@ -1,0 +1,65 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and rejects bad
+arguments with the documented negative codes before touching the device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope='module')
+def lib():
+    from tilekernels_b200 import _lib, build
+    build.build()
+    return _lib.lib()
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, 'include', 'tkquant.h')).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return sorted(set(re.findall(r'\b(tkq_[a-z0-9_]+)\s*\(', text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = _declared_functions()
+    assert 'tkq_per_token_cast' in names and len(names) >= 8
+    for name in names:
+        assert hasattr(lib, name), f'{name} is declared in include/tkquant.h but not exported'
+
+
+def test_binding_covers_header():
+    from tilekernels_b200 import _lib
+    assert set(_declared_functions()) == set(_lib.SIGNATURES) | {'tkq_last_error_string'}
+
+
+def test_version_and_error_text(lib):
+    assert lib.tkq_version() >= 100
+    assert isinstance(lib.tkq_last_error_string(), bytes)
+
+
+def test_argument_checks_need_no_device(lib):
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) // 16 * 16
+    # zero tokens: success, nothing launched
+    assert lib.tkq_per_token_cast(p16, 0, 0, 256, 256, 0, 128, 0, p16, p16, 2, None) == 0
+    # unknown dtype / format
+    assert lib.tkq_per_token_cast(p16, 7, 4, 256, 256, 0, 128, 0, p16, p16, 2, None) == -1
+    assert lib.tkq_per_token_cast(p16, 0, 4, 256, 256, 9, 128, 0, p16, p16, 2, None) == -1
+    # null pointer
+    assert lib.tkq_per_token_cast(None, 0, 4, 256, 256, 0, 128, 0, p16, p16, 2, None) == -1
+    # unsupported group size, hidden not a multiple of 16, packed scales without the column-major flag
+    assert lib.tkq_per_token_cast(p16, 0, 4, 256, 256, 0, 48, 0, p16, p16, 2, None) == -2
+    assert lib.tkq_per_token_cast(p16, 0, 4, 248, 248, 0, 128, 0, p16, p16, 2, None) == -2
+    assert lib.tkq_per_token_cast(p16, 0, 4, 256, 256, 0, 128, 4, p16, p16, 16, None) == -2
+    assert b'column-major' in lib.tkq_last_error_string()
+    # misaligned input
+    assert lib.tkq_per_token_cast(p16 + 2, 0, 4, 256, 256, 0, 128, 0, p16, p16, 2, None) == -3
+    # e5m6 needs one group per token; per-channel needs whole 128-token blocks
+    assert lib.tkq_per_token_cast(p16, 0, 4, 256, 256, 2, 128, 0, p16, p16, 1, None) == -2
+    assert lib.tkq_per_channel_cast(p16, 0, 100, 128, 0, p16, p16, None) == -2
+    assert lib.tkq_per_block_cast(p16, 0, 4, 256, 0, 64, 64, 0, p16, p16, 2, None) == -2
+    assert lib.tkq_swiglu_forward_and_per_token_cast(p16, 0, 4, 192, 128, None, None, None, -1.0, None, -1.0, 0, 0, p16, p16, 1,
+                                                     None) == -2

@@ -1,0 +1,141 @@
+"""The CUDA kernels against the reference-generated fixtures directly (no oracle in between), and the
+benchmark workloads at full size through size-independent properties."""
+import hashlib
+import json
+import os
+
+import pytest
+import torch
+
+from helpers import FLAG_SETS, GOLDEN, flags_id, golden, golden_tensor, to_host
+from tilekernels_b200.testing import assert_equal, make_config_input
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(quant, x, fmt, bs, kw):
+    if bs[0] == 1:
+        return quant.per_token_cast(x, fmt, bs[1], **kw)
+    if bs[1] == 1:
+        return quant.per_channel_cast(x, fmt, bs[0], kw['round_sf'])
+    return quant.per_block_cast(x, fmt, bs, **kw)
+
+
+def _cases():
+    for name in ('bf16_33x320', 'fp32_9x192', 'bf16_130x128'):
+        for fmt in ('e4m3', 'e2m1'):
+            for bs in ((1, 32), (1, 64), (1, 128), (1, 0), (128, 128), (32, 32)):
+                for flags in FLAG_SETS:
+                    yield pytest.param(name, fmt, bs, flags, id=f'{name}-{fmt}-{bs[0]}x{bs[1]}-{flags_id(flags)}')
+
+
+@pytest.mark.parametrize('name,fmt,bs,flags', list(_cases()))
+def test_cast_fixture(cuda_device, name, fmt, bs, flags):
+    from tilekernels_b200 import quant
+    store = golden('cast')
+    x = golden_tensor(store, f'{name}/x')
+    H = x.shape[1]
+    bs = (bs[0], bs[1] or H)
+    if bs[0] == 1 and bs[1] == H and H % 64 != 0:
+        pytest.skip('one scale per token needs hidden % 64 == 0')
+    col, rnd, ue = flags
+    key = f'{name}/{fmt}/{bs[0]}x{bs[1]}/{flags_id(flags)}'
+    out, sf = _call(quant, x.to(cuda_device), fmt, bs, dict(use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue))
+    assert_equal(to_host(out), golden_tensor(store, key + '/out'))
+    assert_equal(to_host(sf), golden_tensor(store, key + '/sf'))
+
+
+@pytest.mark.parametrize('flags', FLAG_SETS, ids=flags_id)
+@pytest.mark.parametrize('name', ['bf16_33x320', 'fp32_9x192'] + [f'{d}_special_{t}' for d in ('bf16', 'fp32')
+                                                                 for t in ('minsub', 'maxsub', 'minnorm')])
+def test_e5m6_fixture(cuda_device, name, flags):
+    from tilekernels_b200 import quant
+    store = golden('e5m6')
+    x = golden_tensor(store, f'{name}/x')
+    col, rnd, ue = flags
+    out, sf = quant.per_token_cast(x.to(cuda_device), 'e5m6', x.shape[1], use_tma_aligned_col_major_sf=col, round_sf=rnd,
+                                   use_packed_ue8m0=ue)
+    key = f'{name}/{flags_id(flags)}'
+    assert_equal(to_host(out), golden_tensor(store, key + '/out'))
+    assert_equal(to_host(sf), golden_tensor(store, key + '/sf'))
+
+
+def test_per_channel_fixture(cuda_device):
+    # [130, 128] is not a multiple of 128 tokens; the first 128 rows form one complete channel block
+    from tilekernels_b200 import quant
+    store = golden('cast')
+    x = golden_tensor(store, 'bf16_130x128/x')[:128].contiguous()
+    for rnd in (False, True):
+        out, sf = quant.per_channel_cast(x.to(cuda_device), 'e4m3', 128, rnd)
+        want_out = golden_tensor(store, f'bf16_130x128/e4m3/128x1/0{int(rnd)}0/out')[:128]
+        want_sf = golden_tensor(store, f'bf16_130x128/e4m3/128x1/0{int(rnd)}0/sf')[:1]
+        assert_equal(to_host(out), want_out.contiguous())
+        assert_equal(to_host(sf), want_sf.contiguous())
+
+
+def _sha(t: torch.Tensor) -> str:
+    t = to_host(t)
+    dense = torch.empty(t.shape, dtype=t.dtype)
+    dense.copy_(t)
+    return hashlib.sha256(dense.flatten().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def _config_ops(quant):
+    return {
+        'cfg1_per_token_e4m3_g128': ('cfg1', lambda x: quant.per_token_cast(x, 'e4m3', 128)),
+        'cfg1_per_token_e4m3_g128_round': ('cfg1', lambda x: quant.per_token_cast(x, 'e4m3', 128, round_sf=True)),
+        'cfg2_per_block_128x128': ('cfg2', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128))),
+        'cfg2_per_channel_128': ('cfg2', lambda x: quant.per_channel_cast(x, 'e4m3', 128)),
+        'cfg4_fp4_g32_ue8m0': ('cfg4', lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)),
+        'cfg4_e5m6': ('cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
+        'cfg5_per_token_e4m3_g128_ue8m0': ('cfg5', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, True, True, True)),
+    }
+
+
+@pytest.mark.parametrize('name', ['cfg1_per_token_e4m3_g128', 'cfg1_per_token_e4m3_g128_round', 'cfg2_per_block_128x128',
+                                  'cfg2_per_channel_128', 'cfg4_fp4_g32_ue8m0', 'cfg4_e5m6', 'cfg5_per_token_e4m3_g128_ue8m0'])
+def test_benchmark_workload_digests(cuda_device, name):
+    """Reduced-row benchmark workloads: the CUDA outputs hash to what the reference produced."""
+    from tilekernels_b200 import quant
+    with open(os.path.join(GOLDEN, 'config_digests.json')) as f:
+        want = json.load(f)[name]
+    cfg, op = _config_ops(quant)[name]
+    x = make_config_input(cfg, want['rows'])
+    assert _sha(x) == want['x']
+    out, sf = op(x.to(cuda_device))
+    assert _sha(out) == want['out']
+    assert _sha(sf) == want['sf']
+
+
+def test_full_size_shard_consistency(cuda_device):
+    """cfg1 at its full size [4096, 7168]: casting the whole tensor equals casting row shards and
+    concatenating (rows are independent), for 1, 2, 4 and 8 shards, and zero rows give zero codes
+    with the clamped scale 1e-4 / 448."""
+    from tilekernels_b200 import quant
+    x = make_config_input('cfg1').to(cuda_device)
+    out, sf = quant.per_token_cast(x, 'e4m3', 128)
+    for k in (2, 4, 8):
+        rows = x.shape[0] // k
+        parts = [quant.per_token_cast(x[i * rows:(i + 1) * rows], 'e4m3', 128) for i in range(k)]
+        assert torch.equal(torch.cat([p[0].view(torch.uint8) for p in parts]), out.view(torch.uint8))
+        assert torch.equal(torch.cat([p[1] for p in parts]), sf)
+    for r in (0, 1023, 2048, 4095):
+        assert int(out[r].view(torch.uint8).max()) == 0
+        assert torch.all(sf[r] == torch.tensor(1e-4, dtype=torch.float32) / 448)
+    # dequantised values reproduce the input to the format's precision (e4m3: 2^-4 relative half-step)
+    dq = out.float() * sf.repeat_interleave(128, dim=1)
+    err = (dq - x.float()).abs()
+    bound = x.float().abs() * 2.0 ** -4 + sf.repeat_interleave(128, dim=1) * 2.0 ** -10
+    assert bool((err <= bound).all())
+
+
+def test_full_size_idempotent_scales(cuda_device):
+    """cfg4 FP4 at 8192 rows: the sf-only pass equals the scales of the full cast, and re-running gives identical bytes."""
+    from tilekernels_b200 import quant
+    x = make_config_input('cfg4', 8192).to(cuda_device)
+    out1, sf1 = quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)
+    out2, sf2 = quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)
+    only = quant.per_token_cast_with_sf_only(x, 'e2m1', 32, None, True, True, True)
+    assert torch.equal(out1, out2)
+    assert torch.equal(to_host(sf1), to_host(sf2)) and torch.equal(to_host(only), to_host(sf1))
+    assert out1.dtype == torch.int8 and sf1.dtype == torch.int32 and sf1.shape == (8192, 56) and sf1.stride() == (1, 8192)

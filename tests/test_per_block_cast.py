@@ -1,0 +1,72 @@
+"""per_block_cast and per_channel_cast on the GPU against the oracle (parametrised as the reference's
+tests/quant/test_per_block_cast.py:38-97 and test_per_channel_cast.py:22-55)."""
+import pytest
+import torch
+
+from helpers import flags_id, to_host
+from tilekernels_b200.testing import assert_equal, check_bias
+
+pytestmark = pytest.mark.gpu
+
+FLAGS = [(False, True, False), (True, True, True), (False, False, False)]
+
+
+def _x(num_tokens, hidden, dtype):
+    g = torch.Generator().manual_seed(num_tokens * 7 + hidden)
+    x = torch.randn((num_tokens, hidden), generator=g)
+    if num_tokens >= 256:
+        x[128:256, :64] *= 50
+        x[200] = 0
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize('flags', FLAGS, ids=flags_id)
+@pytest.mark.parametrize('block', [(128, 128), (32, 32), (128, 32), (32, 128)], ids=lambda b: f'{b[0]}x{b[1]}')
+@pytest.mark.parametrize('fmt', ['e4m3', 'e2m1'])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32], ids=['bf16', 'fp32'])
+@pytest.mark.parametrize('num_tokens,hidden', [(4001, 576), (4001, 2048), (1025, 7168), (129, 2560), (31, 3072), (1, 64)])
+def test_per_block_cast(oracle, cuda_device, num_tokens, hidden, dtype, fmt, block, flags):
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    if block[0] != block[1] and (dtype == torch.float32 or ue):
+        pytest.skip('mixed block shapes: covered for bf16 with fp32 scales')
+    x_cpu = _x(num_tokens, hidden, dtype)
+    x = x_cpu.to(cuda_device)
+    kw = dict(use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue)
+    out, sf = quant.per_block_cast(x, fmt, block, **kw)
+    out_ref, sf_ref = oracle.cast(x_cpu, fmt, block, **kw)
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)
+    if rnd and not col and num_tokens > 1000:
+        check_bias(oracle.cast_back((out_ref, sf_ref), 'fp32', block), x_cpu.float())
+    if not col:
+        pre = quant.per_block_cast_with_precomputed_sf(x, fmt, block, sf=sf, **kw)
+        assert_equal(to_host(pre), oracle.cast(x_cpu, fmt, block, sf=sf_ref))
+    only = quant.per_block_cast_with_sf_only(x, fmt, block, **kw)
+    assert_equal(to_host(only), sf_ref)
+
+
+@pytest.mark.parametrize('round_sf', [False, True])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32], ids=['bf16', 'fp32'])
+@pytest.mark.parametrize('num_tokens,hidden', [(4096, 576), (4096, 2048), (1024, 7168), (128, 2560), (8064, 64), (256, 6144)])
+def test_per_channel_cast(oracle, cuda_device, num_tokens, hidden, dtype, round_sf):
+    from tilekernels_b200 import quant
+    x_cpu = _x(num_tokens, hidden, dtype)
+    out, sf = quant.per_channel_cast(x_cpu.to(cuda_device), 'e4m3', 128, round_sf)
+    out_ref, sf_ref = oracle.cast(x_cpu, 'e4m3', (128, 1), round_sf=round_sf)
+    assert_equal(to_host(out), out_ref)
+    assert_equal(to_host(sf), sf_ref)
+    if round_sf:
+        check_bias(oracle.cast_back((out_ref, sf_ref), 'fp32', (128, 1)), x_cpu.float())
+
+
+def test_tile_kernels_report_no_wait_failure(cuda_device):
+    # the bounded tile wait never ran out during the tests above
+    from tilekernels_b200 import _lib
+    assert _lib.lib().tkq_device_error() == 0
+
+
+def test_per_channel_cast_rejects_ragged_tokens(cuda_device):
+    from tilekernels_b200 import quant
+    with pytest.raises(AssertionError):
+        quant.per_channel_cast(torch.zeros((100, 128), dtype=torch.bfloat16, device=cuda_device), 'e4m3', 128)

@@ -1,0 +1,118 @@
+"""per_token_cast on the GPU against the CPU oracle, bit for bit.
+
+Parametrisation follows the reference's tests/quant/test_per_token_cast.py:50-141 (token counts with
+ragged tails, its hidden sizes, both tested flag sets, strided input, sf-only and precomputed-sf modes)
+and adds the API-default flags (no rounding), which the reference never tests."""
+import pytest
+import torch
+
+from helpers import flags_id, to_host
+from tilekernels_b200.testing import assert_equal, check_bias
+
+pytestmark = pytest.mark.gpu
+
+FLAGS = [(False, True, False), (True, True, True), (False, False, False), (True, False, False)]
+_inputs = {}
+
+
+def make_input(num_tokens, hidden, dtype):
+    key = (num_tokens, hidden, dtype)
+    if key not in _inputs:
+        g = torch.Generator().manual_seed(num_tokens * 131 + hidden)
+        x = torch.randn((num_tokens, hidden), generator=g)
+        if num_tokens > 4:
+            x[1] = 0               # all-zero row -> clamped scale
+            x[2] *= 100            # outlier row
+            x[3, ::7] = -0.0
+        _inputs.clear()            # keep one input alive at a time
+        _inputs[key] = x.to(dtype)
+    return _inputs[key]
+
+
+def _params():
+    for num_tokens, hiddens in ((4001, (576, 2048, 7168)), (129, (2560, 3072, 4096, 6144)), (1, (64,)), (3, (576,))):
+        for hidden in hiddens:
+            for dtype in (torch.bfloat16, torch.float32):
+                for g in (32, 64, 128, hidden):
+                    for fmt in ('e4m3', 'e2m1'):
+                        for flags in FLAGS:
+                            if num_tokens == 129 and flags == (True, False, False):
+                                continue
+                            yield pytest.param(num_tokens, hidden, dtype, g, fmt, flags,
+                                               id=f'{num_tokens}x{hidden}-{str(dtype)[6:]}-g{g}-{fmt}-{flags_id(flags)}')
+    yield pytest.param(257, 1024, torch.bfloat16, 16, 'e4m3', (False, True, False), id='257x1024-bfloat16-g16-e4m3-010')
+    yield pytest.param(257, 1024, torch.float32, 16, 'e2m1', (True, True, True), id='257x1024-float32-g16-e2m1-111')
+
+
+@pytest.mark.parametrize('num_tokens,hidden,dtype,g,fmt,flags', list(_params()))
+def test_per_token_cast(oracle, cuda_device, num_tokens, hidden, dtype, g, fmt, flags):
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    x_cpu = make_input(num_tokens, hidden, dtype)
+    x = x_cpu.to(cuda_device)
+    kw = dict(use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue)
+
+    out, sf = quant.per_token_cast(x, fmt, g, **kw)
+    out_ref, sf_ref = oracle.cast(x_cpu, fmt, (1, g), **kw)
+    assert_equal(to_host(out), out_ref)
+    assert_equal(to_host(sf), sf_ref)
+
+    if rnd and not col:
+        check_bias(oracle.cast_back((out_ref, sf_ref), 'fp32', (1, g)), x_cpu.float())
+
+    # rows strided by twice the hidden size (reference test: test_per_token_cast.py:115-125)
+    if fmt == 'e4m3' and not ue:
+        wide = torch.randn((num_tokens, hidden * 2), device=cuda_device).to(dtype)
+        view = wide[:, :hidden]
+        view.copy_(x)
+        out2, sf2 = quant.per_token_cast(view, fmt, g, **kw)
+        assert_equal(out2, out)
+        assert_equal(to_host(sf2), to_host(sf))
+
+    if g != hidden:
+        if not col:
+            pre = quant.per_token_cast_with_precomputed_sf(x, fmt, g, sf=sf, **kw)
+            assert_equal(to_host(pre), oracle.cast(x_cpu, fmt, (1, g), sf=sf_ref))
+        only = quant.per_token_cast_with_sf_only(x, fmt, g, **kw)
+        assert_equal(to_host(only), sf_ref)
+
+
+def test_per_token_cast_empty(cuda_device):
+    # zero tokens: no launch, correctly shaped outputs (reference: per_token_cast_kernel.py:208, common.py:187-188)
+    from tilekernels_b200 import quant
+    x = torch.empty((0, 256), dtype=torch.bfloat16, device=cuda_device)
+    out, sf = quant.per_token_cast(x, 'e4m3', 128)
+    assert out.shape == (0, 256) and out.dtype == torch.float8_e4m3fn and sf.shape == (0, 2) and sf.dtype == torch.float32
+    out, sf = quant.per_token_cast(x, 'e2m1', 32, use_tma_aligned_col_major_sf=True, round_sf=True, use_packed_ue8m0=True)
+    assert out.shape == (0, 128) and out.dtype == torch.int8 and sf.shape == (0, 2) and sf.dtype == torch.int32
+    out, sf = quant.per_token_cast(x, 'e5m6', 256)
+    assert out.shape == (0, 384) and out.dtype == torch.uint8
+
+
+def test_per_token_cast_rejects_bad_arguments(cuda_device):
+    # argument errors surface as AssertionError before any launch, as in the reference's wrappers
+    from tilekernels_b200 import quant
+    x = torch.zeros((4, 256), dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(AssertionError):
+        quant.per_token_cast(x, 'e4m3', 48)
+    with pytest.raises(AssertionError):
+        quant.per_token_cast(x.half(), 'e4m3', 128)
+    with pytest.raises(AssertionError):
+        quant.per_token_cast(x, 'e3m4', 128)
+    with pytest.raises(AssertionError):
+        quant.per_token_cast(x, 'e4m3', 128, use_packed_ue8m0=True)  # packed scales exist only column-major
+    with pytest.raises(AssertionError):
+        quant.per_token_cast(x, 'e5m6', 128)
+
+
+def test_misaligned_view_uses_narrow_loads(oracle, cuda_device):
+    # a view that starts 16 bytes into a row is only 16-byte aligned: the 128-bit load path must give the same bytes
+    from tilekernels_b200 import quant
+    g = torch.Generator().manual_seed(5)
+    base = torch.randn((65, 1024 + 8), generator=g).to(torch.bfloat16)
+    x_cpu = base[:, 8:]
+    x = base.to(cuda_device)[:, 8:]
+    out, sf = quant.per_token_cast(x, 'e4m3', 128, round_sf=True)
+    out_ref, sf_ref = oracle.cast(x_cpu, 'e4m3', (1, 128), round_sf=True)
+    assert_equal(to_host(out), out_ref)
+    assert_equal(to_host(sf), sf_ref)

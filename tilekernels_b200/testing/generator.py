@@ -36,41 +36,49 @@ def generate_e5m6_inputs(num_tokens: int, hidden: int, dtype: torch.dtype, devic
         yield x, True
 
 
-def make_config_input(name: str, num_tokens: int = None, chunk_rows: int = 4096) -> torch.Tensor:
-    """Seeded CPU bf16 input of a benchmark workload, optionally with fewer rows (same per-row law).
+def make_config_input(name: str, num_tokens: int = None, first_row: int = 0, chunk_rows: int = 4096,
+                      out: torch.Tensor = None) -> torch.Tensor:
+    """Seeded CPU bf16 input of a benchmark workload: rows [first_row, first_row + num_tokens) of
 
     cfg1  [4096, 7168]   N(0,1), 0.1% of entries x100, rows 0/1023/2048/4095 zero          seed 0
     cfg2  [7168, 2048]   N(0, 0.02), block rows 384:512 x cols 640:768 x1000                seed 2
     cfg3  [16384, 4096]  N(0,1) (gate | up halves)                                          seed 1
     cfg4  [32768, 7168]  Student-t(4) * 0.5                                                 seed 4
     cfg5  [262144, 7168] as cfg1 without zero rows                                          seed 5
-    """
+
+    The tensor is defined chunk by chunk (4096 rows, generator seeded with seed * 1000003 + chunk index), so any
+    row range can be produced without drawing the rows before it: ranks generate their own shards.
+    `first_row` must be a multiple of `chunk_rows`.  `out` may be a preallocated (e.g. pinned) destination."""
     shapes = {'cfg1': (4096, 7168), 'cfg2': (7168, 2048), 'cfg3': (16384, 4096), 'cfg4': (32768, 7168),
               'cfg5': (262144, 7168)}
     seeds = {'cfg1': 0, 'cfg2': 2, 'cfg3': 1, 'cfg4': 4, 'cfg5': 5}
-    rows, cols = shapes[name]
-    rows = rows if num_tokens is None else num_tokens
-    g = torch.Generator().manual_seed(seeds[name])
-    out = torch.empty((rows, cols), dtype=torch.bfloat16)
+    total_rows, cols = shapes[name]
+    rows = total_rows - first_row if num_tokens is None else num_tokens
+    assert first_row % chunk_rows == 0
+    if out is None:
+        out = torch.empty((rows, cols), dtype=torch.bfloat16)
+    assert out.shape == (rows, cols) and out.dtype == torch.bfloat16
     for r0 in range(0, rows, chunk_rows):
         n = min(chunk_rows, rows - r0)
+        g0 = first_row + r0  # global row of the chunk start
+        g = torch.Generator().manual_seed(seeds[name] * 1000003 + g0 // chunk_rows)
         if name in ('cfg1', 'cfg5'):
             x = torch.randn((n, cols), generator=g)
             mask = torch.rand((n, cols), generator=g) < 1e-3
             x = torch.where(mask, x * 100, x)
+            if name == 'cfg1':
+                for r in (0, 1023, 2048, 4095):
+                    if g0 <= r < g0 + n:
+                        x[r - g0] = 0
         elif name == 'cfg2':
             x = torch.randn((n, cols), generator=g) * 0.02
-            lo, hi = max(384, r0), min(512, r0 + n)
+            lo, hi = max(384, g0), min(512, g0 + n)
             if lo < hi:
-                x[lo - r0:hi - r0, 640:768] *= 1000
+                x[lo - g0:hi - g0, 640:768] *= 1000
         elif name == 'cfg3':
             x = torch.randn((n, cols), generator=g)
         else:
             z = torch.randn((5, n, cols), generator=g)
             x = z[0] / torch.sqrt((z[1:] ** 2).mean(dim=0)) * 0.5
         out[r0:r0 + n] = x.to(torch.bfloat16)
-    if name == 'cfg1':
-        for r in (0, 1023, 2048, 4095):
-            if r < rows:
-                out[r] = 0
     return out
