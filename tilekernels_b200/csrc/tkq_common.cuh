@@ -75,6 +75,28 @@ struct Scale {
     uint32_t e8;
 };
 
+template <int FMT>
+struct FmtTraits;
+template <>
+struct FmtTraits<TKQ_FMT_E4M3> {
+    static constexpr float kMax = 448.0f;           // 1.75 * 2^8
+    static constexpr uint32_t kMantCarry = 0x1FFFFFu;  // 0x800000 - mantissa(1.75) - 1
+    static constexpr uint32_t kMaxExp = 8;
+};
+template <>
+struct FmtTraits<TKQ_FMT_E2M1> {
+    static constexpr float kMax = 6.0f;  // 1.5 * 2^2
+    static constexpr uint32_t kMantCarry = 0x3FFFFFu;
+    static constexpr uint32_t kMaxExp = 2;
+};
+template <>
+struct FmtTraits<TKQ_FMT_E5M6> {
+    static constexpr float kMax = 65024.0f;  // 1.984375 * 2^15
+    static constexpr uint32_t kMantCarry = 0x01FFFFu;
+    static constexpr uint32_t kMaxExp = 15;
+};
+
+// General form, any clamp and both rounding modes.
 __device__ __forceinline__ Scale make_scale(float amax, float clamp_min, float max_q, bool round_sf) {
     Scale s;
     const float a = fmaxf(amax, clamp_min);
@@ -94,6 +116,34 @@ __device__ __forceinline__ Scale make_scale(float amax, float clamp_min, float m
     return s;
 }
 
+// Power-of-two scales without the division.  With MAX = c * 2^p (1 <= c < 2) and a = m * 2^E:
+// ceil(log2(RN(a / MAX))) = E - p + (m > c), so the biased exponent is ((bits(a) + kMantCarry) >> 23) - p.
+// Equal to make_scale(..., round_sf = true) for every fp32 a with a / MAX normal (checked exhaustively on
+// the CPU for the three formats); the caller guarantees that through clamp_min >= MAX * 2^-126.
+template <int FMT>
+__device__ __forceinline__ Scale make_scale_pow2(float amax, float clamp_min) {
+    Scale s;
+    const uint32_t bits = __float_as_uint(fmaxf(amax, clamp_min));
+    const uint32_t e = ((bits + FmtTraits<FMT>::kMantCarry) >> 23) - FmtTraits<FMT>::kMaxExp;
+    s.sf = __uint_as_float(e << 23);
+    s.inv = __uint_as_float((254u - e) << 23);
+    s.e8 = e;
+    return s;
+}
+
+// kFast: the host established round_sf && clamp_min >= MAX * 2^-126.
+template <int FMT>
+__device__ __forceinline__ Scale make_scale_for(float amax, float clamp_min, bool round_sf, bool fast_pow2) {
+    return fast_pow2 ? make_scale_pow2<FMT>(amax, clamp_min) : make_scale(amax, clamp_min, FmtTraits<FMT>::kMax, round_sf);
+}
+
+// max(|a|, |b|, |c|) in one instruction (three-input max of sm_100)
+__device__ __forceinline__ float max3_abs(float a, float b, float c) {
+    float d;
+    asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Where a scale goes (reference: tile_kernels/quant/common.py:238-244 store_sf).
 // m = token-block index, k = channel-block index.
 __device__ __forceinline__ void store_sf_f32(void* sf, int64_t sf_stride, bool col_major, int64_t m, int64_t k,
@@ -111,6 +161,16 @@ __device__ __forceinline__ float load_sf_f32_row_major(const void* sf, int64_t s
 __device__ __forceinline__ void store_sf_ue8m0_word(void* sf, int64_t sf_stride, int64_t m, int64_t kq, uint32_t word) {
     uint8_t* p = static_cast<uint8_t*>(sf) + kq * sf_stride + 4 * m;
     *reinterpret_cast<uint32_t*>(p) = word;
+}
+
+// One exponent byte of the packed layout.  When k is the last channel block the remaining bytes of its
+// word are zeroed, so that the padding of the layout is deterministic.
+__device__ __forceinline__ void store_sf_ue8m0_byte(void* sf, int64_t sf_stride, int64_t m, uint32_t k, uint32_t num_k,
+                                                    uint32_t e8) {
+    uint8_t* p = static_cast<uint8_t*>(sf) + static_cast<int64_t>(k >> 2) * sf_stride + 4 * m;
+    p[k & 3] = static_cast<uint8_t>(e8);
+    if (k == num_k - 1)
+        for (uint32_t b = (k & 3) + 1; b < 4; ++b) p[b] = 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -159,34 +219,28 @@ __device__ __forceinline__ void pack_e5m6x8(const uint32_t* c, uint32_t* w) {
 }
 
 // ---------------------------------------------------------------------------
-// exp(x) from IEEE add/mul/fma only, so that the CPU checker (oracle/tkq_oracle.c,
-// tkq_expf) reproduces it bit for bit; CUDA's own expf goes through the
-// hardware ex2 approximation, which no CPU can reproduce.  Within 1 ulp.
+// exp(x) from IEEE add/mul/fma and integer operations only, so that the CPU checker
+// (oracle/tkq_oracle.c, tkq_expf: same operations in the same order) reproduces it bit for bit;
+// CUDA's own expf goes through the hardware ex2 approximation, which no CPU can reproduce.
+// Argument clamped to [-87, 88]; within 1 ulp there; 18 instructions.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float tkq_expf(float x) {
-    if (!(x < 88.72284f)) return x != x ? x : __int_as_float(0x7f800000);
-    if (x < -104.0f) return 0.0f;
+    x = fminf(fmaxf(x, -87.0f), 88.0f);
     const float shift = 12582912.0f;
-    const float jf = __fsub_rn(__fmaf_rn(x, 1.4426950408889634f, shift), shift);
-    const float rh = __fmaf_rn(jf, -0.693145751953125f, x);
-    const float rl = __fmul_rn(jf, -1.428606765330187e-06f);
-    const float r = __fadd_rn(rh, rl);
-    const float rc = __fadd_rn(__fsub_rn(rh, r), rl);
-    float q = 2.4801587301587302e-05f;
-    q = __fmaf_rn(q, r, 1.9841269841269841e-04f);
-    q = __fmaf_rn(q, r, 1.3888888888888889e-03f);
-    q = __fmaf_rn(q, r, 8.3333333333333332e-03f);
-    q = __fmaf_rn(q, r, 4.1666666666666664e-02f);
-    q = __fmaf_rn(q, r, 1.6666666666666666e-01f);
-    q = __fmaf_rn(q, r, 0.5f);
+    const float t = __fmaf_rn(x, 1.4426950408889634f, shift);
+    const float jf = __fsub_rn(t, shift);
+    float r = __fmaf_rn(jf, -0.693145751953125f, x);
+    r = __fmaf_rn(jf, -1.428606765330187e-06f, r);
+    float q = 0.001381455804221332f;
+    q = __fmaf_rn(q, r, 0.008368736132979393f);
+    q = __fmaf_rn(q, r, 0.04166838899254799f);
+    q = __fmaf_rn(q, r, 0.1666652113199234f);
+    q = __fmaf_rn(q, r, 0.4999999403953552f);
     const float wl = __fmul_rn(__fmul_rn(r, r), q);
     const float s = __fadd_rn(1.0f, r);
     const float e = __fadd_rn(__fsub_rn(1.0f, s), r);
-    float p = __fadd_rn(s, __fadd_rn(__fadd_rn(e, rc), wl));
-    const int j = static_cast<int>(jf);
-    const int j1 = j / 2, j2 = j - j1;
-    p = __fmul_rn(p, __uint_as_float(static_cast<uint32_t>(j1 + 127) << 23));
-    return __fmul_rn(p, __uint_as_float(static_cast<uint32_t>(j2 + 127) << 23));
+    const float p = __fadd_rn(s, __fadd_rn(e, wl));
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 // silu(g) * u evaluated as (g / (1 + exp(-g))) * u with IEEE division

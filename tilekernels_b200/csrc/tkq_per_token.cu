@@ -8,12 +8,15 @@ namespace tkq {
 
 template <int DT, int FMT, int LPG>
 static int launch_group(const TokenCastParams& p, cudaStream_t stream) {
-    constexpr int U = DT == TKQ_DT_BF16 ? 4 : 2;
-    auto kernel = group_cast_kernel<PlainSource<DT>, false, FMT, LPG, U, 0>;
-    const int64_t warps_needed = (static_cast<int64_t>(p.total_items) + U - 1) / U;
-    const int grid = grid_size(kernel, kGroupThreads, (warps_needed + kGroupThreads / 32 - 1) / (kGroupThreads / 32), 0);
-    kernel<<<grid, kGroupThreads, 0, stream>>>(p);
-    return check_launch("per_token_cast (group kernel)");
+    const char* what = "per_token_cast (group kernel)";
+    // bytes per lane and step: 32 (bf16) or 64 (fp32)
+    // measured on B200: many resident warps with one step each beat fewer warps with several steps in flight;
+    // FP4 (half the output bytes per step) prefers two
+    const int u = group_unroll((DT == TKQ_DT_BF16 && FMT == TKQ_FMT_E2M1) ? 2 : 1, DT == TKQ_DT_BF16 ? 4 : 2);
+    if (u == 4) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, (DT == TKQ_DT_BF16 ? 4 : 2), 0>, p,
+                                           DT == TKQ_DT_BF16 ? 4 : 2, 0, stream, what);
+    if (u == 2) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, 2, 0>, p, 2, 0, stream, what);
+    return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, 1, 0>, p, 1, 0, stream, what);
 }
 
 template <int DT, int FMT>
@@ -121,17 +124,13 @@ extern "C" int tkq_per_token_cast(const void* x, int in_dtype, int64_t num_token
     p.flags = flags;
     p.clamp_min = fmt == TKQ_FMT_E4M3 ? 1e-4f : 6.0f * 1.1754943508222875e-38f;  // 6 * 2^-126
     p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((x_row_stride * elem) % 32 == 0);
+    p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, fmt == TKQ_FMT_E4M3 ? 448.0f : 6.0f);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
     const bool group_kernel = num_per_channels == 16 || num_per_channels == 32 || num_per_channels == 64 ||
                               num_per_channels == 128;
     if (group_kernel) {
-        const int64_t steps = (hidden + 511) / 512;
-        if (num_tokens * steps >= (int64_t{1} << 31))
-            return set_error(TKQ_E_UNSUPPORTED, "per_token_cast: more than 2^31 work items; split the token dimension");
-        p.steps_per_row = static_cast<uint32_t>(steps);
         p.num_groups = static_cast<uint32_t>((hidden + num_per_channels - 1) / num_per_channels);
-        p.total_items = static_cast<uint32_t>(num_tokens * steps);
         if (in_dtype == TKQ_DT_BF16)
             return fmt == TKQ_FMT_E4M3 ? dispatch_group<TKQ_DT_BF16, TKQ_FMT_E4M3>(p, num_per_channels, s)
                                        : dispatch_group<TKQ_DT_BF16, TKQ_FMT_E2M1>(p, num_per_channels, s);
@@ -178,6 +177,7 @@ extern "C" int tkq_per_token_cast_e5m6(const void* x, int in_dtype, int64_t num_
     p.flags = flags;
     p.clamp_min = 1e-4f;
     p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((x_row_stride * elem) % 32 == 0);
+    p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 65024.0f);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return in_dtype == TKQ_DT_BF16 ? dispatch_e5m6<TKQ_DT_BF16>(p, s) : dispatch_e5m6<TKQ_DT_FP32>(p, s);
 }

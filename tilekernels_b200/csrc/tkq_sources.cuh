@@ -125,9 +125,11 @@ struct SwigluSource {
                 ui = ui > clamp ? clamp : ui;
                 ui = ui < -clamp ? -clamp : ui;
             }
-            float y = swiglu(gi, ui);
-            if (kWeight) y = __fmul_rn(y, w);
-            v[i] = y;
+            v[i] = swiglu(gi, ui);
+        }
+        if (kWeight && w != 1.0f) {  // uniform over the row; multiplying by exactly 1 would change nothing
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], w);
         }
     }
 };
@@ -138,7 +140,7 @@ struct SwigluSource {
 __device__ __forceinline__ float absmax16(const float* v) {
     float m = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    for (int i = 0; i < 16; i += 2) m = max3_abs(m, v[i], v[i + 1]);
     return m;
 }
 

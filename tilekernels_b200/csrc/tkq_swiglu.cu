@@ -6,13 +6,12 @@ namespace tkq {
 
 template <int DT, int kClampMode>
 static int launch_swiglu_group(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
-    constexpr int U = DT == TKQ_DT_BF16 ? 2 : 1;  // two input streams per item
-    auto kernel = group_cast_kernel<SwigluSource<DT>, true, TKQ_FMT_E4M3, 8, U, kClampMode>;
-    const int64_t warps_needed = (static_cast<int64_t>(p.total_items) + U - 1) / U;
-    const int grid = grid_size(kernel, kGroupThreads, (warps_needed + kGroupThreads / 32 - 1) / (kGroupThreads / 32), 0,
-                               sm_limit);
-    kernel<<<grid, kGroupThreads, 0, stream>>>(p);
-    return check_launch("swiglu_forward_and_per_token_cast (group kernel)");
+    const char* what = "swiglu_forward_and_per_token_cast (group kernel)";
+    // two input streams per step: 64 (bf16) or 128 (fp32) bytes per lane and step
+    const int u = group_unroll(1, DT == TKQ_DT_BF16 ? 2 : 1);
+    if (u == 2) return launch_group_kernel(group_cast_kernel<SwigluSource<DT>, true, TKQ_FMT_E4M3, 8, (DT == TKQ_DT_BF16 ? 2 : 1), kClampMode>,
+                                           p, DT == TKQ_DT_BF16 ? 2 : 1, sm_limit, stream, what);
+    return launch_group_kernel(group_cast_kernel<SwigluSource<DT>, true, TKQ_FMT_E4M3, 8, 1, kClampMode>, p, 1, sm_limit, stream, what);
 }
 
 template <int DT, int kClampMode, int K>
@@ -87,12 +86,8 @@ extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype
     p.pos_to_expert = pos_to_expert;
     p.swiglu_clamp = swiglu_clamp;
     p.clamped_count = reinterpret_cast<unsigned long long*>(clamped_count);
-    const int64_t steps = (hidden + 511) / 512;
-    if (num_tokens * steps >= (int64_t{1} << 31))
-        return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: more than 2^31 work items; split the token dimension");
-    p.steps_per_row = static_cast<uint32_t>(steps);
     p.num_groups = per_row_scale ? 1u : static_cast<uint32_t>(hidden / 128);
-    p.total_items = static_cast<uint32_t>(num_tokens * steps);
+    p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 448.0f);
     const int sm_limit = clamped_count != nullptr ? num_sms : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return in_dtype == TKQ_DT_BF16 ? dispatch_clamp<TKQ_DT_BF16>(p, per_row_scale, sm_limit, s)

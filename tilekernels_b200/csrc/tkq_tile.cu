@@ -1,11 +1,15 @@
-// Per-block and per-channel casts: 128 x 128 tiles staged in shared memory by the
-// bulk-copy engine (TMA, untiled form: one cp.async.bulk per tile row, all
-// completing on a single mbarrier; no tensor map and no multicast).
+// Per-block and per-channel casts: 128 x 128 tiles staged in shared memory by TMA
+// (cp.async.bulk.tensor.2d, one instruction per tile completing on an mbarrier; no
+// multicast).  Blocks are persistent and keep several tile loads in flight
+// (run_tile_pipeline).
 //
 // Thread mapping inside a tile (256 threads): thread t owns the 16-column chunk
 // c16 = t % 8 of rows t / 8 + 32 * i, i = 0..3.  A warp therefore covers 4 full
 // rows per i, reads shared memory in whole rows and writes 4 x 128 B of e4m3 per
 // store instruction.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include "tkq_launch.cuh"
 #include "tkq_sources.cuh"
 
@@ -43,11 +47,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-// global -> shared bulk copy; both addresses 16-byte aligned, bytes a multiple of 16
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+// One TMA tile load: the (128 x 128)-element box at column `x`, row `y` of the tensor described by `tmap`
+// lands in shared memory; elements outside the tensor arrive as zeros and count towards the barrier's
+// byte count.  x * element size is a multiple of 16 bytes (x is a multiple of 128).
+__device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap* tmap, int32_t x, int32_t y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                      smem_u32(smem_dst)),
-                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
 
@@ -58,14 +64,18 @@ struct TileParams {
     int64_t num_tokens;
     int64_t hidden;
     int64_t sf_stride;
-    uint32_t tiles_k;  // tiles along the channel dimension
+    uint32_t tiles_k;    // tiles along the channel dimension
+    uint32_t num_tiles;  // tiles_k * ceil(num_tokens / 128)
+    uint32_t stages;     // shared-memory tile buffers per block
     uint32_t flags;
     float clamp_min;
+    bool fast_pow2;
 };
 
 template <int DT>
 struct TileElem {
     static constexpr int kBytes = DT == TKQ_DT_BF16 ? 2 : 4;
+    static constexpr int kTileBytes = kTile * kTile * kBytes;
 };
 
 // Reads the thread's 16 values of tile row `r` from shared memory.
@@ -92,226 +102,287 @@ __device__ __forceinline__ void read_chunk(const uint8_t* tile, int r, int c16, 
     }
 }
 
-// Stages the tile (rows0.., cols0..) of x into shared memory and waits for it.
-// Returns false (after raising the device error flag) if the wait ran out.
+// Where tile number `tile` sits in the tensor.
+struct TileCoord {
+    int64_t tile_m, tile_k, row0, col0;
+    int valid_rows, valid_cols;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const TileParams& p, uint32_t tile) {
+    TileCoord c;
+    c.tile_m = tile / p.tiles_k;
+    c.tile_k = tile - c.tile_m * p.tiles_k;
+    c.row0 = c.tile_m * kTile;
+    c.col0 = c.tile_k * kTile;
+    c.valid_rows = static_cast<int>(p.num_tokens - c.row0 < kTile ? p.num_tokens - c.row0 : kTile);
+    c.valid_cols = static_cast<int>(p.hidden - c.col0 < kTile ? p.hidden - c.col0 : kTile);
+    return c;
+}
+
+// Called by one thread: arms the stage's barrier with the tile's byte count and issues the tile load.
 template <int DT>
-__device__ __forceinline__ bool stage_tile(const TileParams& p, uint8_t* tile, uint64_t* bar, int64_t row0, int64_t col0,
-                                           int valid_rows, int valid_cols) {
-    constexpr int EB = TileElem<DT>::kBytes;
-    const int t = threadIdx.x;
-    if (t == 0) mbar_init(bar, 1);
+__device__ __forceinline__ void issue_tile(const TileParams& p, const CUtensorMap* tmap, uint32_t tile, uint8_t* stage,
+                                           uint64_t* bar) {
+    const TileCoord c = tile_coord(p, tile);
+    mbar_arrive_expect_tx(bar, TileElem<DT>::kTileBytes);
+    tma_load_tile(stage, tmap, static_cast<int32_t>(c.col0), static_cast<int32_t>(c.row0), bar);
+}
+
+// The tile pipeline shared by both kernels.  Blocks are persistent: block b handles tiles b, b + grid, ...;
+// thread 0 keeps `stages` tile loads in flight; a stage is refilled as soon as every thread has copied its
+// part of the tile into registers.  `consume(i, coord, v)` does the arithmetic of one tile; it contains
+// block-wide barriers, so every thread calls it.
+template <int DT, class Consume>
+__device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUtensorMap* tmap, uint8_t* smem, uint64_t* full_bar,
+                                                  Consume consume) {
+    const uint32_t t = threadIdx.x;
+    const uint32_t stages = p.stages;
+    if (t == 0) {
+        for (uint32_t s = 0; s < stages; ++s) mbar_init(full_bar + s, 1);
+    }
     __syncthreads();
-    const uint32_t row_bytes = static_cast<uint32_t>(valid_cols) * EB;
-    if (t == 0) mbar_arrive_expect_tx(bar, row_bytes * static_cast<uint32_t>(valid_rows));
-    if (t < valid_rows) {
-        const uint8_t* src = static_cast<const uint8_t*>(p.x) + ((row0 + t) * p.hidden + col0) * EB;
-        bulk_load(tile + static_cast<size_t>(t) * kTile * EB, src, row_bytes, bar);
+    const uint32_t first = blockIdx.x, step = gridDim.x;
+    const uint32_t my_tiles = first < p.num_tiles ? (p.num_tiles - first + step - 1) / step : 0;
+    if (t == 0) {
+        for (uint32_t i = 0; i < stages && i < my_tiles; ++i)
+            issue_tile<DT>(p, tmap, first + i * step, smem + static_cast<size_t>(i) * TileElem<DT>::kTileBytes, full_bar + i);
     }
-    if (!mbar_wait(bar, 0)) {
-        atomicExch(&g_tile_wait_failed, 1u);
-        return false;
+    const int c16 = t & 7, r_base = t >> 3;
+    for (uint32_t i = 0; i < my_tiles; ++i) {
+        const uint32_t s = i % stages, parity = (i / stages) & 1;
+        const TileCoord c = tile_coord(p, first + i * step);
+        if (!mbar_wait(full_bar + s, parity)) {
+            atomicExch(&g_tile_wait_failed, 1u);
+            return;
+        }
+        const uint8_t* tile = smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes;
+        float v[4][16];
+        const bool col_ok = c16 * 16 < c.valid_cols;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (col_ok && r < c.valid_rows) {
+                read_chunk<DT>(tile, r, c16, v[k]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[k][j] = 0.0f;
+            }
+        }
+        // the reads above went through the generic proxy, the refill below goes through the async proxy:
+        // order them before the barrier that lets thread 0 overwrite the stage
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();  // the stage is free again
+        if (t == 0 && i + stages < my_tiles)
+            issue_tile<DT>(p, tmap, first + (i + stages) * step, smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes, full_bar + s);
+        consume(i, c, v, col_ok);
     }
-    return true;
 }
 
 // ---------------------------------------------------------------------------
 // Per-block cast: one scale per (BM x BK) block, BM, BK in {32, 128}.
 // ---------------------------------------------------------------------------
 template <int DT, int FMT, int BM, int BK>
-__global__ void __launch_bounds__(kTileThreads) per_block_cast_kernel(const TileParams p) {
-    constexpr float kMaxQ = FMT == TKQ_FMT_E4M3 ? 448.0f : 6.0f;
+__global__ void __launch_bounds__(kTileThreads) per_block_cast_kernel(const __grid_constant__ CUtensorMap tmap, const TileParams p) {
     constexpr int NRB = kTile / BM, NCB = kTile / BK;  // scale blocks per tile
     constexpr int kLanesPerCb = BK / 16;                // lanes of a row that share a column block (2 or 8)
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* tile = smem;
-    __shared__ uint64_t bar;
-    __shared__ int amax_bits[NRB * NCB];
+    __shared__ uint64_t full_bar[8];
+    __shared__ int amax_bits[2][NRB * NCB];  // double-buffered by tile parity
 
     const int t = threadIdx.x, lane = t & 31;
     const int c16 = t & 7, r_base = t >> 3;
-    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
-    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
-    const int valid_rows = static_cast<int>(p.num_tokens - row0 < kTile ? p.num_tokens - row0 : kTile);
-    const int valid_cols = static_cast<int>(p.hidden - col0 < kTile ? p.hidden - col0 : kTile);
     const bool round_sf = p.flags & TKQ_ROUND_SF;
     const bool cast_only = p.flags & TKQ_CAST_ONLY;
     const bool sf_only = p.flags & TKQ_SF_ONLY;
-
-    if (t < NRB * NCB) amax_bits[t] = 0;
-    if (!stage_tile<DT>(p, tile, &bar, row0, col0, valid_rows, valid_cols)) return;
-
-    const bool col_ok = c16 * 16 < valid_cols;
     const int cb = c16 * 16 / BK;
-    float v[4][16];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = r_base + 32 * i;
-        if (col_ok && r < valid_rows) {
-            read_chunk<DT>(tile, r, c16, v[i]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[i][j] = 0.0f;
-        }
-    }
-
-    const int64_t sf_m0 = row0 / BM, sf_k0 = col0 / BK;
     const int64_t num_kb = (p.hidden + BK - 1) / BK;
-    float inv[4];
-    if (cast_only) {
+    if (t < 2 * NRB * NCB) (&amax_bits[0][0])[t] = 0;
+
+    run_tile_pipeline<DT>(p, &tmap, smem, full_bar, [&](uint32_t i, const TileCoord& c, float (&v)[4][16], bool col_ok) {
+        int* amax = amax_bits[i & 1];
+        const int64_t sf_m0 = c.row0 / BM, sf_k0 = c.col0 / BK;
+        float inv[4];
+        if (cast_only) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int rb = (r_base + 32 * i) / BM;
-            const bool ok = col_ok && (r_base + 32 * i) < valid_rows;
-            inv[i] = ok ? __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, sf_m0 + rb, sf_k0 + cb)) : 0.0f;
-        }
-    } else {
-        // maxima per row block, combined over the lanes and warps that share the block
-        float m[NRB];
+            for (int k = 0; k < 4; ++k) {
+                const int rb = (r_base + 32 * k) / BM;
+                const bool ok = col_ok && (r_base + 32 * k) < c.valid_rows;
+                inv[k] = ok ? __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, sf_m0 + rb, sf_k0 + cb)) : 0.0f;
+            }
+        } else {
+            // maxima per row block, combined over the lanes and warps that share the block
+            float m[NRB];
 #pragma unroll
-        for (int rb = 0; rb < NRB; ++rb) m[rb] = 0.0f;
+            for (int rb = 0; rb < NRB; ++rb) m[rb] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int rb = NRB == 1 ? 0 : i;  // BM = 32: rows r_base + 32 i lie in row block i
-            m[rb] = fmaxf(m[rb], absmax16(v[i]));
-        }
+            for (int k = 0; k < 4; ++k) {
+                const int rb = NRB == 1 ? 0 : k;  // BM = 32: rows r_base + 32 k lie in row block k
+                m[rb] = fmaxf(m[rb], absmax16(v[k]));
+            }
 #pragma unroll
-        for (int rb = 0; rb < NRB; ++rb) {
+            for (int rb = 0; rb < NRB; ++rb) {
 #pragma unroll
-            for (int o = kLanesPerCb / 2; o > 0; o >>= 1) m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], o));
-            m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], 8));
-            m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], 16));
-            if (lane < 8 && (lane % kLanesPerCb) == 0) atomicMax(&amax_bits[rb * NCB + cb], __float_as_int(m[rb]));
-        }
-        __syncthreads();
+                for (int o = kLanesPerCb / 2; o > 0; o >>= 1) m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], o));
+                m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], 8));
+                m[rb] = fmaxf(m[rb], __shfl_xor_sync(kFullMask, m[rb], 16));
+                if (lane < 8 && (lane % kLanesPerCb) == 0) atomicMax(&amax[rb * NCB + cb], __float_as_int(m[rb]));
+            }
+            __syncthreads();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int rb = NRB == 1 ? 0 : i;
-            const Scale s = make_scale(__int_as_float(amax_bits[rb * NCB + cb]), p.clamp_min, kMaxQ, round_sf);
-            inv[i] = s.inv;
-        }
-        // one thread per scale block stores it
-        if (t < NRB * NCB) {
-            const int rb = t / NCB, kb = t % NCB;
-            const int64_t m_idx = sf_m0 + rb, k_idx = sf_k0 + kb;
-            if (rb * BM < valid_rows && kb * BK < valid_cols) {
-                const Scale s = make_scale(__int_as_float(amax_bits[t]), p.clamp_min, kMaxQ, round_sf);
-                if (p.flags & TKQ_SF_UE8M0) {
-                    uint8_t* base = static_cast<uint8_t*>(p.sf) + (k_idx >> 2) * p.sf_stride + 4 * m_idx;
-                    base[k_idx & 3] = static_cast<uint8_t>(s.e8);
-                    if (k_idx == num_kb - 1)  // zero the unused bytes of the last word
-                        for (int64_t b = (k_idx & 3) + 1; b < 4; ++b) base[b] = 0;
+            for (int k = 0; k < 4; ++k) {
+                const int rb = NRB == 1 ? 0 : k;
+                if (NRB == 1 && k > 0) {
+                    inv[k] = inv[0];
                 } else {
-                    store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, m_idx, k_idx, s.sf);
+                    inv[k] = make_scale_for<FMT>(__int_as_float(amax[rb * NCB + cb]), p.clamp_min, round_sf, p.fast_pow2).inv;
                 }
             }
+            // one thread per scale block stores it
+            if (t < NRB * NCB) {
+                const int rb = t / NCB, kb = t % NCB;
+                const int64_t m_idx = sf_m0 + rb, k_idx = sf_k0 + kb;
+                if (rb * BM < c.valid_rows && kb * BK < c.valid_cols) {
+                    const Scale s = make_scale_for<FMT>(__int_as_float(amax[t]), p.clamp_min, round_sf, p.fast_pow2);
+                    if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_byte(p.sf, p.sf_stride, m_idx, static_cast<uint32_t>(k_idx), static_cast<uint32_t>(num_kb), s.e8);
+                    else store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, m_idx, k_idx, s.sf);
+                }
+            }
+            // this tile's maxima were all read before the next tile's first barrier; clear the other buffer for it
+            if (t < NRB * NCB) amax_bits[(i + 1) & 1][t] = 0;
         }
-    }
-    if (sf_only) return;
+        if (sf_only) return;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = r_base + 32 * i;
-        if (col_ok && r < valid_rows) {
-            const int64_t col = col0 + c16 * 16;
-            if constexpr (FMT == TKQ_FMT_E4M3) quantize_store_e4m3x16(v[i], inv[i], p.out + (row0 + r) * p.hidden + col);
-            else quantize_store_e2m1x16(v[i], inv[i], p.out + (row0 + r) * (p.hidden / 2) + col / 2);
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (col_ok && r < c.valid_rows) {
+                const int64_t col = c.col0 + c16 * 16;
+                if constexpr (FMT == TKQ_FMT_E4M3) quantize_store_e4m3x16(v[k], inv[k], p.out + (c.row0 + r) * p.hidden + col);
+                else quantize_store_e2m1x16(v[k], inv[k], p.out + (c.row0 + r) * (p.hidden / 2) + col / 2);
+            }
         }
-    }
+    });
 }
 
 // ---------------------------------------------------------------------------
 // Per-channel cast: one scale per (128 tokens x 1 channel); e4m3 only.
 // ---------------------------------------------------------------------------
 template <int DT>
-__global__ void __launch_bounds__(kTileThreads) per_channel_cast_kernel(const TileParams p) {
+__global__ void __launch_bounds__(kTileThreads) per_channel_cast_kernel(const __grid_constant__ CUtensorMap tmap, const TileParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* tile = smem;
-    __shared__ uint64_t bar;
-    __shared__ int col_amax_bits[kTile];
+    __shared__ uint64_t full_bar[8];
+    __shared__ int col_amax_bits[2][kTile];
     __shared__ float col_inv[kTile];
 
     const int t = threadIdx.x, lane = t & 31;
     const int c16 = t & 7, r_base = t >> 3;
-    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
-    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
-    const int valid_rows = static_cast<int>(p.num_tokens - row0 < kTile ? p.num_tokens - row0 : kTile);
-    const int valid_cols = static_cast<int>(p.hidden - col0 < kTile ? p.hidden - col0 : kTile);
     const bool round_sf = p.flags & TKQ_ROUND_SF;
+    (&col_amax_bits[0][0])[t] = 0;  // 256 threads, 2 x 128 entries
 
-    if (t < kTile) col_amax_bits[t] = 0;
-    if (!stage_tile<DT>(p, tile, &bar, row0, col0, valid_rows, valid_cols)) return;
-
-    const bool col_ok = c16 * 16 < valid_cols;
-    float v[4][16];
-    float cm[16];
+    run_tile_pipeline<DT>(p, &tmap, smem, full_bar, [&](uint32_t i, const TileCoord& c, float (&v)[4][16], bool col_ok) {
+        int* col_amax = col_amax_bits[i & 1];
+        float cm[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) cm[j] = 0.0f;
+        for (int j = 0; j < 16; ++j) cm[j] = max3_abs(fabsf(v[0][j]), v[1][j], max3_abs(0.0f, v[2][j], v[3][j]));
+        // combine the 4 rows a warp holds per chunk, then the 8 warps through shared-memory atomics
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = r_base + 32 * i;
-        if (col_ok && r < valid_rows) {
-            read_chunk<DT>(tile, r, c16, v[i]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[i][j] = 0.0f;
+        for (int j = 0; j < 16; ++j) {
+            cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 8));
+            cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 16));
         }
+        if (lane < 8) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) cm[j] = fmaxf(cm[j], fabsf(v[i][j]));
-    }
-    // combine the 4 rows a warp holds per chunk, then the 8 warps through shared-memory atomics
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 8));
-        cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 16));
-    }
-    if (lane < 8) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) atomicMax(&col_amax_bits[c16 * 16 + j], __float_as_int(cm[j]));
-    }
-    __syncthreads();
-    if (t < kTile) {
-        const Scale s = make_scale(__int_as_float(col_amax_bits[t]), p.clamp_min, 448.0f, round_sf);
-        col_inv[t] = s.inv;
-        if (t < valid_cols) static_cast<float*>(p.sf)[tile_m * p.hidden + col0 + t] = s.sf;
-    }
-    __syncthreads();
-    float inv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) inv[j] = col_inv[c16 * 16 + j];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = r_base + 32 * i;
-        if (col_ok && r < valid_rows) {
-            float s[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) s[j] = __fmul_rn(v[i][j], inv[j]);
-            stg128(p.out + (row0 + r) * p.hidden + col0 + c16 * 16, cvt_e4m3x4(s[0], s[1], s[2], s[3]),
-                   cvt_e4m3x4(s[4], s[5], s[6], s[7]), cvt_e4m3x4(s[8], s[9], s[10], s[11]),
-                   cvt_e4m3x4(s[12], s[13], s[14], s[15]));
+            for (int j = 0; j < 16; ++j) atomicMax(&col_amax[c16 * 16 + j], __float_as_int(cm[j]));
         }
-    }
+        __syncthreads();
+        if (t < kTile) {
+            const Scale s = make_scale_for<TKQ_FMT_E4M3>(__int_as_float(col_amax[t]), p.clamp_min, round_sf, p.fast_pow2);
+            col_inv[t] = s.inv;
+            if (t < c.valid_cols) static_cast<float*>(p.sf)[c.tile_m * p.hidden + c.col0 + t] = s.sf;
+            col_amax_bits[(i + 1) & 1][t] = 0;
+        }
+        __syncthreads();
+        float inv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) inv[j] = col_inv[c16 * 16 + j];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (col_ok && r < c.valid_rows) {
+                float q[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) q[j] = __fmul_rn(v[k][j], inv[j]);
+                stg128(p.out + (c.row0 + r) * p.hidden + c.col0 + c16 * 16, cvt_e4m3x4(q[0], q[1], q[2], q[3]),
+                       cvt_e4m3x4(q[4], q[5], q[6], q[7]), cvt_e4m3x4(q[8], q[9], q[10], q[11]),
+                       cvt_e4m3x4(q[12], q[13], q[14], q[15]));
+            }
+        }
+    });
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }();
+    return fn;
+}
+
+// Describes x as a [num_tokens, hidden] row-major tensor read in 128 x 128 boxes, out-of-range elements as zeros.
+static int make_tensor_map(CUtensorMap* tmap, const void* x, int elem_bytes, int64_t num_tokens, int64_t hidden) {
+    auto encode = tensor_map_encoder();
+    if (encode == nullptr) return set_error(TKQ_E_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hidden), static_cast<cuuint64_t>(num_tokens)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hidden) * elem_bytes};
+    const cuuint32_t box[2] = {kTile, kTile};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = encode(tmap, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                              const_cast<void*>(x), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(TKQ_E_UNSUPPORTED, "cuTensorMapEncodeTiled rejected the tensor (alignment or size)");
+    return 0;
+}
+
+// Launch geometry: persistent blocks, two per SM, each with up to three tile buffers (about 100 KB).
 template <class Kernel>
-static int launch_tile(Kernel kernel, const TileParams& p, int elem_bytes, const char* what, cudaStream_t stream) {
-    const int smem = kTile * kTile * elem_bytes;
-    if (smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
-    }
+static int launch_tile(Kernel kernel, TileParams p, int elem_bytes, const char* what, cudaStream_t stream) {
+    const int tile_bytes = kTile * kTile * elem_bytes;
     const int64_t tiles = ((p.num_tokens + kTile - 1) / kTile) * p.tiles_k;
-    if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
-    kernel<<<static_cast<unsigned>(tiles), kTileThreads, smem, stream>>>(p);
+    if (tiles >= (int64_t{1} << 31) || p.num_tokens >= (int64_t{1} << 31))
+        return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
+    alignas(64) CUtensorMap tmap;
+    if (int rc = make_tensor_map(&tmap, p.x, elem_bytes, p.num_tokens, p.hidden)) return rc;
+    const int sms = device_sm_count();
+    const int blocks_per_sm = 2;
+    const int grid = static_cast<int>(tiles < static_cast<int64_t>(sms) * blocks_per_sm ? tiles : static_cast<int64_t>(sms) * blocks_per_sm);
+    const int max_stages = (100 * 1024) / tile_bytes;  // 3 bf16 tiles or 1 fp32 tile
+    const int64_t tiles_per_block = (tiles + grid - 1) / grid;
+    int stages = static_cast<int>(tiles_per_block < max_stages ? tiles_per_block : max_stages);
+    if (stages < 1) stages = 1;
+    p.num_tiles = static_cast<uint32_t>(tiles);
+    p.stages = static_cast<uint32_t>(stages);
+    const int smem = stages * tile_bytes;
+    static thread_local Kernel configured = nullptr;
+    if (configured != kernel) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
+        configured = kernel;
+    }
+    kernel<<<grid, kTileThreads, smem, stream>>>(tmap, p);
     return check_launch(what);
 }
 
 template <int DT, int FMT>
 static int dispatch_block(const TileParams& p, int bm, int bk, cudaStream_t s) {
-    constexpr int EB = TileElem<DT>::kBytes;
+    constexpr int TB = TileElem<DT>::kBytes;
     const char* what = "per_block_cast";
-    if (bm == 128 && bk == 128) return launch_tile(per_block_cast_kernel<DT, FMT, 128, 128>, p, EB, what, s);
-    if (bm == 32 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 32, 32>, p, EB, what, s);
-    if (bm == 128 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 128, 32>, p, EB, what, s);
-    if (bm == 32 && bk == 128) return launch_tile(per_block_cast_kernel<DT, FMT, 32, 128>, p, EB, what, s);
+    if (bm == 128 && bk == 128) return launch_tile(per_block_cast_kernel<DT, FMT, 128, 128>, p, TB, what, s);
+    if (bm == 32 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 32, 32>, p, TB, what, s);
+    if (bm == 128 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 128, 32>, p, TB, what, s);
+    if (bm == 32 && bk == 128) return launch_tile(per_block_cast_kernel<DT, FMT, 32, 128>, p, TB, what, s);
     return set_error(TKQ_E_UNSUPPORTED, "per_block_cast: block sizes must be 32 or 128");
 }
 
@@ -353,6 +424,7 @@ extern "C" int tkq_per_block_cast(const void* x, int in_dtype, int64_t num_token
     p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
     p.flags = flags;
     p.clamp_min = fmt == TKQ_FMT_E4M3 ? 1e-4f : 6.0f * 1.1754943508222875e-38f;
+    p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (in_dtype == TKQ_DT_BF16)
         return fmt == TKQ_FMT_E4M3 ? dispatch_block<TKQ_DT_BF16, TKQ_FMT_E4M3>(p, block_m, block_k, s)
@@ -382,6 +454,7 @@ extern "C" int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tok
     p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
     p.flags = flags;
     p.clamp_min = 1e-4f;
+    p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return in_dtype == TKQ_DT_BF16
                ? launch_tile(per_channel_cast_kernel<TKQ_DT_BF16>, p, 2, "per_channel_cast", s)

@@ -10,6 +10,9 @@
 // row_cast_kernel handles one scale per row, reduced across the thread block.
 #pragma once
 
+#include <cstdlib>
+
+#include "tkq_launch.cuh"
 #include "tkq_sources.cuh"
 
 namespace tkq {
@@ -22,13 +25,16 @@ struct TokenCastParams {
     int64_t sf_stride;   // see tkquant.h
     int64_t out_stride;  // bytes between rows of out
     int64_t num_tokens;
-    int64_t hidden;        // values per row that are quantized (SwiGLU: half the input columns)
-    uint32_t steps_per_row;  // ceil(hidden / 512)
+    int64_t hidden;          // values per row that are quantized (SwiGLU: half the input columns)
+    uint32_t items_per_row;  // work items per row; an item is U consecutive 512-value steps
     uint32_t num_groups;     // scale groups per row
-    uint32_t total_items;    // num_tokens * steps_per_row
+    uint32_t total_items;    // num_tokens * items_per_row
+    uint32_t stride_rows;    // (warps in the grid) / items_per_row   -- the step of the grid-stride loop,
+    uint32_t stride_items;   // (warps in the grid) % items_per_row      split so the loop needs no division
     uint32_t flags;
     float clamp_min;
     bool wide_loads;  // every row of x starts on a 32-byte boundary: 256-bit loads are legal
+    bool fast_pow2;   // round_sf with a clamp that keeps the scale normal: division-free scale path
     // SwiGLU only
     const int32_t* pos_to_token_topk;
     const float* topk_weights;
@@ -38,17 +44,6 @@ struct TokenCastParams {
 };
 
 constexpr int kGroupThreads = 256;
-
-template <int FMT>
-struct FmtTraits;
-template <>
-struct FmtTraits<TKQ_FMT_E4M3> {
-    static constexpr float kMax = 448.0f;
-};
-template <>
-struct FmtTraits<TKQ_FMT_E2M1> {
-    static constexpr float kMax = 6.0f;
-};
 
 __device__ __forceinline__ void flush_clamp_counters(const ClampCounters& cnt, unsigned long long* dst) {
     uint32_t a = cnt.gate_hi, b = cnt.up_hi, c = cnt.up_lo;
@@ -68,8 +63,6 @@ __device__ __forceinline__ void flush_clamp_counters(const ClampCounters& cnt, u
 // kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count (SwiGLU sources only)
 template <class Src, bool kSwiglu, int FMT, int LPG, int U, int kClampMode>
 __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCastParams p) {
-    constexpr float kMaxQ = FmtTraits<FMT>::kMax;
-    constexpr int kLanesPerWord = 4 * LPG;  // lanes that share one packed ue8m0 word (may exceed 32: LPG = 8 -> 32)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -79,76 +72,69 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
     const bool sf_only = p.flags & TKQ_SF_ONLY;
     const bool cast_only = p.flags & TKQ_CAST_ONLY;
     const bool wide = p.wide_loads;
+    const bool fast_pow2 = p.fast_pow2;
+    const uint32_t hidden = static_cast<uint32_t>(p.hidden);
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
     ClampCounters cnt;
 
-    for (uint32_t base = warp; base < p.total_items; base += nwarps * U) {
+    uint32_t row = warp / p.items_per_row;
+    uint32_t sub = warp - row * p.items_per_row;
+    for (uint32_t item = warp; item < p.total_items; item += nwarps) {
+        const uint32_t col0 = sub * (512u * U) + lane * 16u;
+        const uint32_t this_row = row;
+        sub += p.stride_items;
+        row += p.stride_rows;
+        if (sub >= p.items_per_row) {
+            sub -= p.items_per_row;
+            ++row;
+        }
+        if (kSwiglu && p.pos_to_expert != nullptr && p.pos_to_expert[this_row] < 0) continue;  // warp-uniform
+
         typename Src::Raw raw[U];
-        uint32_t row[U], col[U];
-        bool live[U];
+        const uint8_t* src = xb + (static_cast<int64_t>(this_row) * p.x_stride + col0) * Src::kElemBytes;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t item = base + u * nwarps;
-            live[u] = item < p.total_items;
-            row[u] = 0;
-            col[u] = 0;
-            if (live[u]) {
-                row[u] = item / p.steps_per_row;
-                col[u] = (item - row[u] * p.steps_per_row) * 512u + lane * 16u;
-                if (kSwiglu && p.pos_to_expert != nullptr && p.pos_to_expert[row[u]] < 0) live[u] = false;
-            }
-            if (live[u] && col[u] < p.hidden) {
-                const uint8_t* src = xb + (static_cast<int64_t>(row[u]) * p.x_stride + col[u]) * Src::kElemBytes;
-                if constexpr (kSwiglu) Src::issue(raw[u], src, wide, p.hidden);
-                else Src::issue(raw[u], src, wide);
+            if (col0 + u * 512u < hidden) {
+                if constexpr (kSwiglu) Src::issue(raw[u], src + u * 512 * Src::kElemBytes, wide, p.hidden);
+                else Src::issue(raw[u], src + u * 512 * Src::kElemBytes, wide);
             } else {
                 Src::zero(raw[u]);
             }
         }
+        float w = 1.0f;
+        if constexpr (kSwiglu) {
+            if (p.pos_to_token_topk != nullptr) {
+                const int32_t pos = p.pos_to_token_topk[this_row];
+                w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
+            }
+        }
+        uint8_t* out_row = p.out + static_cast<int64_t>(this_row) * p.out_stride;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (!live[u]) continue;  // warp-uniform
+            const uint32_t col = col0 + u * 512u;
+            if (U > 1 && col - lane * 16u >= hidden) break;  // warp-uniform: the whole step lies beyond the row
             float v[16];
-            if constexpr (kSwiglu) {
-                float w = 1.0f;
-                if (p.pos_to_token_topk != nullptr) {
-                    const int32_t pos = p.pos_to_token_topk[row[u]];
-                    w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
-                }
-                Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt);
-            } else {
-                Src::unpack(raw[u], v);
-            }
-            const bool in_row = col[u] < p.hidden;
-            const uint32_t g = col[u] / (16u * LPG);
+            if constexpr (kSwiglu) Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt);
+            else Src::unpack(raw[u], v);
+            const bool in_row = col < hidden;
+            const uint32_t g = col / (16u * LPG);
             float inv;
             if (cast_only) {
-                inv = in_row ? __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, row[u], g)) : 0.0f;
+                inv = in_row ? __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, this_row, g)) : 0.0f;
             } else {
                 float amax = absmax16(v);
 #pragma unroll
                 for (int o = LPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, o));
-                const Scale s = make_scale(amax, p.clamp_min, kMaxQ, round_sf);
+                const Scale s = make_scale_for<FMT>(amax, p.clamp_min, round_sf, fast_pow2);
                 inv = s.inv;
-                if (ue8m0) {
-                    uint32_t word = 0;
-                    const uint32_t g0 = g & ~3u;
-                    const uint32_t lane0 = kLanesPerWord >= 32 ? 0u : (lane & ~static_cast<uint32_t>(kLanesPerWord - 1));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint32_t b = __shfl_sync(kFullMask, s.e8, lane0 + k * LPG);
-                        if (g0 + k < p.num_groups) word |= b << (8 * k);
-                    }
-                    if (lane == lane0 && g < p.num_groups) store_sf_ue8m0_word(p.sf, p.sf_stride, row[u], g >> 2, word);
-                } else if (lane % LPG == 0 && in_row) {
-                    store_sf_f32(p.sf, p.sf_stride, col_major, row[u], g, s.sf);
+                if (lane % LPG == 0 && in_row) {
+                    if (ue8m0) store_sf_ue8m0_byte(p.sf, p.sf_stride, this_row, g, p.num_groups, s.e8);
+                    else store_sf_f32(p.sf, p.sf_stride, col_major, this_row, g, s.sf);
                 }
             }
             if (!sf_only && in_row) {
-                if constexpr (FMT == TKQ_FMT_E4M3)
-                    quantize_store_e4m3x16(v, inv, p.out + static_cast<int64_t>(row[u]) * p.out_stride + col[u]);
-                else
-                    quantize_store_e2m1x16(v, inv, p.out + static_cast<int64_t>(row[u]) * p.out_stride + col[u] / 2);
+                if constexpr (FMT == TKQ_FMT_E4M3) quantize_store_e4m3x16(v, inv, out_row + col);
+                else quantize_store_e2m1x16(v, inv, out_row + col / 2);
             }
         }
     }
@@ -182,7 +168,6 @@ __device__ __forceinline__ void store_row_scale(const TokenCastParams& p, int64_
 
 template <class Src, bool kSwiglu, int FMT, int K, int kClampMode>
 __global__ void __launch_bounds__(kRowMaxThreads) row_cast_kernel(const TokenCastParams p) {
-    constexpr float kMaxQ = FmtTraits<FMT>::kMax;
     __shared__ float red[2][32];
     const bool round_sf = p.flags & TKQ_ROUND_SF;
     const bool wide = p.wide_loads;
@@ -222,7 +207,7 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_kernel(const TokenCas
         }
         amax = block_max(amax, red, parity);
         parity ^= 1;
-        const Scale s = make_scale(amax, p.clamp_min, kMaxQ, round_sf);
+        const Scale s = make_scale_for<FMT>(amax, p.clamp_min, round_sf, p.fast_pow2);
         if (threadIdx.x == 0) store_row_scale(p, row, s);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
@@ -315,12 +300,12 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_e5m6_kernel(const Tok
                 float v[8];
                 L::unpack(raw[k][o], v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                for (int i = 0; i < 8; i += 2) amax = max3_abs(amax, v[i], v[i + 1]);
             }
         }
         amax = block_max(amax, red, parity);
         parity ^= 1;
-        const Scale s = make_scale(amax, p.clamp_min, 65024.0f, round_sf);
+        const Scale s = make_scale_for<TKQ_FMT_E5M6>(amax, p.clamp_min, round_sf, p.fast_pow2);
         if (threadIdx.x == 0) store_row_scale(p, row, s);
         uint32_t* out_row = reinterpret_cast<uint32_t*>(p.out + row * p.out_stride);
 #pragma unroll
@@ -357,6 +342,42 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_e5m6_kernel(const Tok
             }
         }
     }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: geometry of a group_cast_kernel launch.
+// ---------------------------------------------------------------------------
+template <class Kernel>
+int launch_group_kernel(Kernel kernel, TokenCastParams p, int unroll, int sm_limit, cudaStream_t stream, const char* what) {
+    const int64_t steps = (p.hidden + 511) / 512;
+    const int64_t items_per_row = (steps + unroll - 1) / unroll;
+    const int64_t total = p.num_tokens * items_per_row;
+    if (total >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "more than 2^31 work items; split the token dimension");
+    constexpr int kWarpsPerBlock = kGroupThreads / 32;
+    const int grid = grid_size(kernel, kGroupThreads, (total + kWarpsPerBlock - 1) / kWarpsPerBlock, 0, sm_limit);
+    const uint32_t nwarps = static_cast<uint32_t>(grid) * kWarpsPerBlock;
+    p.items_per_row = static_cast<uint32_t>(items_per_row);
+    p.total_items = static_cast<uint32_t>(total);
+    p.stride_rows = nwarps / p.items_per_row;
+    p.stride_items = nwarps % p.items_per_row;
+    kernel<<<grid, kGroupThreads, 0, stream>>>(p);
+    return check_launch(what);
+}
+
+// Steps per work item.  TKQ_GROUP_UNROLL (1, 2 or 4) overrides the default; a tuning aid.
+inline int group_unroll(int dflt, int max_unroll) {
+    static const int forced = [] {
+        const char* e = std::getenv("TKQ_GROUP_UNROLL");
+        return e ? std::atoi(e) : 0;
+    }();
+    int u = forced > 0 ? forced : dflt;
+    if (u > max_unroll) u = max_unroll;
+    return u >= 4 ? 4 : (u >= 2 ? 2 : 1);
+}
+
+// round_sf with a clamp that keeps clamp / MAX a normal number: the division-free scale path applies.
+inline bool can_use_fast_pow2(unsigned flags, float clamp_min, float max_q) {
+    return (flags & TKQ_ROUND_SF) && clamp_min >= max_q * 1.1754943508222875e-38f;
 }
 
 }  // namespace tkq
