@@ -35,9 +35,9 @@ GROUP = 128
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 # DRAM bytes per token of the dominant kernel from the ncu capture summarised in
-# profiles/per_token_cast_e4m3_ue8m0.md (dram__bytes_read.sum + dram__bytes_write.sum per launch / rows);
-# None until a capture exists.
-NCU_DRAM_BYTES_PER_TOKEN = None
+# profiles/per_token_cast_e4m3_ue8m0_cfg5.md: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch
+# over 32768 rows / 32768.  Traffic is proportional to the row count, so a launch's traffic is this x rows.
+NCU_DRAM_BYTES_PER_TOKEN = 20465
 
 
 def bytes_per_token() -> int:
@@ -256,6 +256,7 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     from tilekernels_b200 import host, quant
+    from tilekernels_b200.sharding import shard_rows
     from tilekernels_b200.testing import count_bytes, make_config_input
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -272,12 +273,13 @@ def run_ours(args) -> None:
             dist.barrier()
 
     total_rows = args.rows or TOTAL_ROWS
-    assert total_rows % (world * 4096) == 0, 'rows must split into whole 4096-row chunks per rank'
-    rows = total_rows // world
+    first_row, last_row = shard_rows(total_rows, rank, world, alignment=4096)  # whole generator chunks per rank
+    rows = last_row - first_row
+    assert rows > 0 and rows % 4 == 0, 'every rank needs rows, in multiples of 4'
 
     # the rank's shard, generated on the host (pinned), then copied once for the device-resident measurement
     x_host = torch.empty((rows, HIDDEN), dtype=torch.bfloat16, pin_memory=True)
-    make_config_input('cfg5', rows, first_row=rank * rows, out=x_host)
+    make_config_input('cfg5', rows, first_row=first_row, out=x_host)
     x = x_host.to(device, non_blocking=True)
     torch.cuda.synchronize()
 

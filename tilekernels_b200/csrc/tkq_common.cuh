@@ -184,8 +184,17 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     return r;
 }
 
+// Four values -> four bytes (a in the lowest).  Both conversions and the merge of the two halves sit in one
+// asm block so that the assembler can write each half of the result register directly.
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-    return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+    uint32_t r;
+    asm("{ .reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi}; }"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+    return r;
 }
 
 // Two values -> one byte, `lo` in the low nibble.
@@ -196,8 +205,16 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
 }
 
 __device__ __forceinline__ uint32_t cvt_e2m1x8(const float* v) {
-    return cvt_e2m1x2(v[0], v[1]) | (cvt_e2m1x2(v[2], v[3]) << 8) | (cvt_e2m1x2(v[4], v[5]) << 16) |
-           (cvt_e2m1x2(v[6], v[7]) << 24);
+    uint32_t r;
+    asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3}; }"
+        : "=r"(r)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return r;
 }
 
 // fp32 -> 12-bit E5M6 code: fp16 with round-toward-zero, cut to 12 bits, then round to
