@@ -217,8 +217,8 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(const float* v) {
     return r;
 }
 
-// fp32 -> 12-bit E5M6 code: fp16 with round-toward-zero, cut to 12 bits, then round to
-// nearest even on the 17 low bits of the fp32
+// fp32 -> 12-bit E5M6 code, the reference's definition: fp16 with round-toward-zero, cut to 12 bits, then
+// round to nearest even on the 17 low bits of the fp32
 // (reference: tile_kernels/quant/per_token_cast_to_e5m6_kernel.py:44-51).
 __device__ __forceinline__ uint32_t cvt_e5m6(float v) {
     const uint32_t h = __half_as_ushort(__float2half_rz(v));
@@ -228,11 +228,42 @@ __device__ __forceinline__ uint32_t cvt_e5m6(float v) {
     return c & 0xFFFu;
 }
 
-// Eight codes -> three words (per_token_cast_to_e5m6_kernel.py:53-64).
+// The same code for 2^-14 <= |v| < 65520 (the fp16-normal range), where the definition above is plain
+// round-to-nearest-even of v to 1+6 significant bits followed by a re-bias of the exponent.  Everything that
+// can run on the floating-point / multiply-add pipe does, because the integer pipe is what limits this cast:
+//   * v is first scaled by 2^-112 (exact in this range), which re-biases the exponent for free;
+//   * the rounding is a Veltkamp split, c = v * (2^17 + 1), hi = c - (c - v): v rounded to nearest even at
+//     7 significant bits (checked against integer RNE for every mantissa of 44 binades on the CPU);
+//   * hi >> 17 is then sign(1) | 000 | exponent(5) | mantissa(6); one multiply-add moves the sign from
+//     bit 14 to bit 11.
+__device__ __forceinline__ uint32_t mad_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t cvt_e5m6_normal(float v) {
+    const float vs = __fmul_rn(v, 1.925929944387236e-34f);  // 2^-112
+    const float c = __fmul_rn(vs, 131073.0f);
+    const float hi = __fsub_rn(c, __fsub_rn(c, vs));
+    const uint32_t bits = __float_as_uint(hi);
+    const uint32_t t = bits >> 17;
+    return mad_u32(bits >> 31, 0u - 0x3800u, t);  // t - sign * (2^14 - 2^11)
+}
+
+// min(|a|, |b|, |c|)
+__device__ __forceinline__ float min3_abs(float a, float b, float c) {
+    float d;
+    asm("min.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Eight codes -> three words (per_token_cast_to_e5m6_kernel.py:53-64).  The fields do not overlap, so every
+// shift-and-or is written as a multiply-add.
 __device__ __forceinline__ void pack_e5m6x8(const uint32_t* c, uint32_t* w) {
-    w[0] = (c[0] << 20) | (c[1] << 8) | (c[2] >> 4);
-    w[1] = (c[2] << 28) | (c[3] << 16) | (c[4] << 4) | (c[5] >> 8);
-    w[2] = (c[5] << 24) | (c[6] << 12) | c[7];
+    w[0] = mad_u32(c[0], 1u << 20, mad_u32(c[1], 1u << 8, c[2] >> 4));
+    w[1] = mad_u32(c[2], 1u << 28, mad_u32(c[3], 1u << 16, mad_u32(c[4], 1u << 4, c[5] >> 8)));
+    w[2] = mad_u32(c[5], 1u << 24, mad_u32(c[6], 1u << 12, c[7]));
 }
 
 // ---------------------------------------------------------------------------

@@ -1,5 +1,6 @@
 // C entry points of the per-token casts (FP8 e4m3, FP4 e2m1, E5M6).
 #include <algorithm>
+#include <cstdlib>
 
 #include "tkq_launch.cuh"
 #include "tkq_token_kernels.cuh"
@@ -58,9 +59,38 @@ static int launch_e5m6(const TokenCastParams& p, int threads, cudaStream_t strea
     return check_launch("per_token_cast_e5m6");
 }
 
+// The bulk-copy row pipeline: rows of hidden % 32 == 0 values that fit a shared-memory ring.
+template <int DT, int K>
+static int launch_e5m6_pipeline(const TokenCastParams& p, int threads, uint32_t stages, uint32_t stage_bytes, cudaStream_t stream) {
+    auto kernel = e5m6_row_pipeline_kernel<DT, K>;
+    const int smem = static_cast<int>(stages * stage_bytes);
+    static thread_local decltype(kernel) configured = nullptr;
+    if (configured != kernel) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
+        configured = kernel;
+    }
+    const int grid = grid_size(kernel, threads, p.num_tokens, smem);
+    kernel<<<grid, threads, smem, stream>>>(p, stages, stage_bytes);
+    return check_launch("per_token_cast_e5m6 (row pipeline)");
+}
+
 template <int DT>
 static int dispatch_e5m6(const TokenCastParams& p, cudaStream_t stream) {
     int k = 0, threads = 0;
+    constexpr int EB = DT == TKQ_DT_BF16 ? 2 : 4;
+    const uint32_t stage_bytes = static_cast<uint32_t>((p.hidden * EB + 127) / 128 * 128);
+    if (p.hidden % 32 == 0 && stage_bytes <= 96 * 1024 && std::getenv("TKQ_E5M6_NO_PIPELINE") == nullptr) {
+        // blocks of about 256 threads so that several blocks (and their rings) share an SM
+        if (row_shape(p.hidden / 16, 256, &k, &threads)) {
+            const uint32_t stages = stage_bytes <= 16 * 1024 ? 3u : 2u;
+            switch (k) {
+                case 1: return launch_e5m6_pipeline<DT, 1>(p, threads, stages, stage_bytes, stream);
+                case 2: return launch_e5m6_pipeline<DT, 2>(p, threads, stages, stage_bytes, stream);
+                default: return launch_e5m6_pipeline<DT, 4>(p, threads, stages, stage_bytes, stream);
+            }
+        }
+    }
     if (!row_shape((p.hidden + 31) / 32, kRowMaxThreads, &k, &threads))
         return set_error(TKQ_E_UNSUPPORTED, "per_token_cast_e5m6: hidden too large (max 65536)");
     switch (k) {
@@ -68,6 +98,13 @@ static int dispatch_e5m6(const TokenCastParams& p, cudaStream_t stream) {
         case 2: return launch_e5m6<DT, 2>(p, threads, stream);
         default: return launch_e5m6<DT, 4>(p, threads, stream);
     }
+}
+
+int row_wait_flag() {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_row_wait_failed, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_row_wait_failed, &zero, sizeof(zero));
+    return static_cast<int>(v);
 }
 
 static int check_sf_flags(unsigned flags, const void* sf, int64_t sf_stride, const char** why) {

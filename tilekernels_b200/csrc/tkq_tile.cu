@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include "tkq_async.cuh"
 #include "tkq_launch.cuh"
 #include "tkq_sources.cuh"
 
@@ -20,42 +21,6 @@ constexpr int kTileThreads = 256;
 
 // Set when a kernel gave up waiting for its tile; read back by tkq_device_error().
 __device__ unsigned int g_tile_wait_failed = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Bounded wait: returns false if the phase did not complete within the poll budget.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (int i = 0; i < (1 << 22); ++i) {
-        uint32_t done;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-// One TMA tile load: the (128 x 128)-element box at column `x`, row `y` of the tensor described by `tmap`
-// lands in shared memory; elements outside the tensor arrive as zeros and count towards the barrier's
-// byte count.  x * element size is a multiple of 16 bytes (x is a multiple of 128).
-__device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap* tmap, int32_t x, int32_t y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                     smem_u32(smem_dst)),
-                 "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
-                 : "memory");
-}
 
 struct TileParams {
     const void* x;
@@ -170,7 +135,7 @@ __device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUt
         }
         // the reads above went through the generic proxy, the refill below goes through the async proxy:
         // order them before the barrier that lets thread 0 overwrite the stage
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_proxy_async_smem();
         __syncthreads();  // the stage is free again
         if (t == 0 && i + stages < my_tiles)
             issue_tile<DT>(p, tmap, first + (i + stages) * step, smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes, full_bar + s);
@@ -392,11 +357,17 @@ using namespace tkq;
 
 // Non-zero if any tile kernel of this process gave up waiting for its staged tile since the
 // last call; reading clears the flag.  Synchronises the device.
-extern "C" int tkq_device_error(void) {
+int tkq::tile_wait_flag() {
     unsigned int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_tile_wait_failed, sizeof(v)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(g_tile_wait_failed, &zero, sizeof(zero));
     return static_cast<int>(v);
+}
+
+extern "C" int tkq_device_error(void) {
+    const int a = tile_wait_flag(), b = row_wait_flag();
+    if (a < 0 || b < 0) return -1;
+    return (a | b) ? 1 : 0;
 }
 
 extern "C" int tkq_per_block_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int fmt, int block_m,

@@ -12,6 +12,7 @@
 
 #include <cstdlib>
 
+#include "tkq_async.cuh"
 #include "tkq_launch.cuh"
 #include "tkq_sources.cuh"
 
@@ -147,6 +148,28 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
 // maximum through shared memory with a single barrier per row.
 // ---------------------------------------------------------------------------
 constexpr int kRowMaxThreads = 512;
+
+// 16 values of a chunk held as raw 16-byte pieces (2 for bf16, 4 for fp32) -> floats.
+template <int DT>
+__device__ __forceinline__ void unpack_chunk(const uint4* raw, float* v) {
+    if constexpr (DT == TKQ_DT_BF16) {
+        const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = bf16_lo(w[i]);
+            v[2 * i + 1] = bf16_hi(w[i]);
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            v[4 * q] = __uint_as_float(raw[q].x);
+            v[4 * q + 1] = __uint_as_float(raw[q].y);
+            v[4 * q + 2] = __uint_as_float(raw[q].z);
+            v[4 * q + 3] = __uint_as_float(raw[q].w);
+        }
+    }
+}
+
 
 __device__ __forceinline__ float block_max(float m, float (*red)[32], int parity) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -342,6 +365,116 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_e5m6_kernel(const Tok
             }
         }
     }
+}
+
+// ---------------------------------------------------------------------------
+// E5M6 with rows staged by the bulk-copy engine (used when hidden % 32 == 0 and a few rows fit in shared
+// memory; row_cast_e5m6_kernel above is the fallback).
+//
+// A block walks rows b, b + grid, ...  Thread 0 keeps `stages - 1` rows ahead in flight: one
+// cp.async.bulk per row into a ring of shared-memory stages, each completing on its own mbarrier.  The
+// block reads a row from its stage, reduces the maximum (barrier 1, after which nobody reads the stage any
+// more), converts, and writes the packed 12-bit codes back into the *same* stage (the output row is 3/4 of
+// the input row).  After barrier 2 thread 0 sends the stage to global memory with one bulk store and
+// refills the stage of the previous row, whose store has finished reading by then.  Loads and stores are
+// asynchronous and fully coalesced, and the registers hold only the row being converted.
+// ---------------------------------------------------------------------------
+static __device__ unsigned int g_row_wait_failed = 0;
+
+template <int DT, int K>
+__global__ void __launch_bounds__(kRowMaxThreads) e5m6_row_pipeline_kernel(const TokenCastParams p, const uint32_t stages,
+                                                                            const uint32_t stage_bytes) {
+    constexpr int EB = DT == TKQ_DT_BF16 ? 2 : 4;
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ uint64_t full_bar[4];
+    __shared__ float red[2][32];
+    const uint32_t t = threadIdx.x;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    const uint32_t in_bytes = static_cast<uint32_t>(p.hidden) * EB;
+    const uint32_t out_bytes = static_cast<uint32_t>(p.out_stride);
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+
+    if (t == 0) {
+        for (uint32_t s = 0; s < stages; ++s) mbar_init(full_bar + s, 1);
+    }
+    __syncthreads();
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t my_rows = first < p.num_tokens ? (p.num_tokens - first + step - 1) / step : 0;
+    auto issue_row = [&](int64_t i) {  // thread 0 only
+        const uint32_t s = static_cast<uint32_t>(i % stages);
+        mbar_arrive_expect_tx(full_bar + s, in_bytes);
+        bulk_load(ring + static_cast<size_t>(s) * stage_bytes, xb + (first + i * step) * p.x_stride * EB, in_bytes, full_bar + s);
+    };
+    if (t == 0) {
+        for (int64_t i = 0; i + 1 < stages && i < my_rows; ++i) issue_row(i);
+    }
+    int parity_red = 0;
+    for (int64_t i = 0; i < my_rows; ++i) {
+        const uint32_t s = static_cast<uint32_t>(i % stages);
+        const int64_t row = first + i * step;
+        uint8_t* stage = ring + static_cast<size_t>(s) * stage_bytes;
+        if (!mbar_wait(full_bar + s, static_cast<uint32_t>(i / stages) & 1u)) {
+            atomicExch(&g_row_wait_failed, 1u);
+            return;
+        }
+        // the thread's K chunks of 16 values
+        float v[K][16];
+        float amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const uint32_t chunk = t + k * blockDim.x;
+            uint4 raw[EB];  // bf16: 2 x 16 bytes per chunk, fp32: 4 x 16 bytes
+            if (chunk * 16 < p.hidden) {
+                const uint4* src = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(chunk) * 16 * EB);
+#pragma unroll
+                for (int q = 0; q < EB; ++q) raw[q] = src[q];
+            } else {
+#pragma unroll
+                for (int q = 0; q < EB; ++q) raw[q] = make_uint4(0, 0, 0, 0);
+            }
+            unpack_chunk<DT>(raw, v[k]);
+            amax = fmaxf(amax, absmax16(v[k]));
+        }
+        amax = block_max(amax, red, parity_red);  // barrier 1: every thread has its part of the row in registers
+        parity_red ^= 1;
+        const Scale sc = make_scale_for<TKQ_FMT_E5M6>(amax, p.clamp_min, round_sf, p.fast_pow2);
+        if (t == 0) store_row_scale(p, row, sc);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const uint32_t chunk = t + k * blockDim.x;
+            if (chunk * 16 >= p.hidden) continue;
+            uint32_t c[16], w[6];
+            float smallest = 1.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[k][j] = __fmul_rn(v[k][j], sc.inv);
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) smallest = min3_abs(smallest, v[k][j], v[k][j + 1]);
+            if (smallest >= 6.103515625e-05f) {  // every |v| >= 2^-14: the fp16-normal rules apply to the whole chunk
+#pragma unroll
+                for (int j = 0; j < 16; ++j) c[j] = cvt_e5m6_normal(v[k][j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) c[j] = cvt_e5m6(v[k][j]);
+            }
+            pack_e5m6x8(c, w);
+            pack_e5m6x8(c + 8, w + 3);
+            uint2* dst = reinterpret_cast<uint2*>(stage + static_cast<size_t>(chunk) * 24);
+            dst[0] = make_uint2(w[0], w[1]);
+            dst[1] = make_uint2(w[2], w[3]);
+            dst[2] = make_uint2(w[4], w[5]);
+        }
+        fence_proxy_async_smem();  // the codes were written through the generic proxy, the store reads through the async proxy
+        __syncthreads();           // barrier 2: the output row is complete in the stage
+        if (t == 0) {
+            bulk_store(p.out + row * p.out_stride, stage, out_bytes);
+            const int64_t next = i + stages - 1;
+            if (next < my_rows) {
+                bulk_store_wait_read<1>();  // the store of the previous row (whose stage is refilled now) has read its data
+                issue_row(next);
+            }
+        }
+    }
+    if (t == 0) bulk_store_wait_all();
 }
 
 // ---------------------------------------------------------------------------
