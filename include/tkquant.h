@@ -84,6 +84,27 @@ int tkq_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t 
                        int64_t num_per_channels, unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream);
 
 /*
+ * Per-token cast of an ALREADY QUANTIZED input: x holds FP8 e4m3 bytes or packed FP4 e2m1 nibbles with one
+ * scale per (x_block_m x x_block_k) block; every value is float(x) * scale (an fp32 product), then cast as in
+ * tkq_per_token_cast.  Replaces the same launch, tile_kernels/quant/per_token_cast_kernel.py:208-209, for the
+ * `with_sf` input configuration (kernel body :87-126; input detection tile_kernels/quant/common.py:62-88).
+ * The data are scaled as (x * scale_in) * inverse_out, the order of the reference's PyTorch implementation
+ * (tile_kernels/torch/cast.py:93-97,174-176); the reference kernel folds the two factors first, which is the
+ * same thing for power-of-two scales, the only case its tests use.
+ *
+ *   x             in_fmt e4m3: [num_tokens, hidden] bytes; e2m1: [num_tokens, hidden / 2] bytes;
+ *                 x_row_stride in VALUES (twice the byte stride for e2m1)
+ *   x_sf          input scales, m = token / x_block_m, k = channel / x_block_k, in the layout given by
+ *                 x_sf_flags (0 = row-major fp32, TKQ_SF_COL_MAJOR, TKQ_SF_COL_MAJOR | TKQ_SF_UE8M0) with
+ *                 x_sf_stride as sf_stride above
+ *   num_per_channels  16, 32, 64 or 128; x_block_k a multiple of 16
+ */
+int tkq_per_token_cast_quantized(const void* x, int in_fmt, const void* x_sf, unsigned x_sf_flags, int64_t x_sf_stride,
+                                 int x_block_m, int x_block_k, int64_t num_tokens, int64_t hidden, int64_t x_row_stride,
+                                 int fmt, int64_t num_per_channels, unsigned flags, void* out, void* sf, int64_t sf_stride,
+                                 void* stream);
+
+/*
  * Per-token cast to E5M6 (12-bit codes, one scale per token, maximum 65024, clamp 1e-4).
  * Replaces the launch in tile_kernels/quant/per_token_cast_to_e5m6_kernel.py:209-210
  * (kernel :108-154, float_to_e5m6 :33-64).
@@ -120,6 +141,26 @@ int tkq_per_block_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t 
  */
 int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, unsigned flags, void* out,
                          void* sf, void* stream);
+
+/*
+ * Fused per-channel cast to e4m3: the per-channel cast (one scale per 128 output tokens x 1 channel) of
+ *   - rows gathered through pos_to_token (out row i = x row pos_to_token[i]; a negative entry = a row of zeros), and/or
+ *   - FP8 e4m3 input with one fp32 scale per (token, 128 channels): every value is float(x) * scale before the
+ *     maximum is taken and the data are written as (x * scale) * inverse.
+ * Replaces the launch in tile_kernels/quant/per_channel_cast_fused_kernel.py:200-201 (kernel :50-132) for the
+ * cases tkq_per_channel_cast does not cover.
+ *
+ *   in_kind        TKQ_DT_BF16, TKQ_DT_FP32, or 2 = FP8 e4m3 bytes (then x_sf is required, hidden % 128 == 0)
+ *   x              [num_tokens_in, hidden], contiguous
+ *   x_sf           [num_tokens_in, hidden / 128] fp32, contiguous (FP8 input only, else NULL)
+ *   pos_to_token   int32[num_tokens_out] or NULL (then num_tokens_out == num_tokens_in, a multiple of 128);
+ *                  with it num_tokens_out must be a multiple of 16
+ *   out            [num_tokens_out, hidden] bytes;  sf  [ceil(num_tokens_out / 128), hidden] fp32
+ * flags: TKQ_ROUND_SF only.
+ */
+int tkq_per_channel_cast_fused(const void* x, int in_kind, const float* x_sf, const int32_t* pos_to_token,
+                               int64_t num_tokens_in, int64_t num_tokens_out, int64_t hidden, unsigned flags, void* out,
+                               void* sf, void* stream);
 
 /*
  * Fused SwiGLU + per-token e4m3 cast: y = silu(x[:, :hidden]) * x[:, hidden:] in fp32

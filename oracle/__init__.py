@@ -79,9 +79,13 @@ def format_sf(bits: torch.Tensor, col_major: bool, packed_ue8m0: bool) -> torch.
 
 def cast(x: torch.Tensor, fmt: str, block_size=(32, 32), sf: Optional[torch.Tensor] = None, round_sf: bool = False,
          use_tma_aligned_col_major_sf: bool = False, use_packed_ue8m0: bool = False,
-         clamp_min: Optional[float] = None):
-    """Same contract as the reference's tile_kernels.torch.cast (cast.py:62-221) for plain
-    bf16/fp32 inputs.  Returns `out` when `sf` is given, else `(out, out_sf)`."""
+         clamp_min: Optional[float] = None, x_block_size=None):
+    """Same contract as the reference's tile_kernels.torch.cast (cast.py:62-221).  An already quantized input
+    `(data, scales)` with `x_block_size` is dequantised to fp32 first (data * scale, cast.py:86-97) and then
+    cast like any fp32 tensor.  Returns `out` when `sf` is given, else `(out, out_sf)`."""
+    if isinstance(x, tuple):
+        assert x_block_size is not None
+        x = cast_back(x, 'fp32', x_block_size)
     x = _rows(x)
     T, H = x.shape
     bm, bk = block_size
@@ -138,6 +142,21 @@ def sf_to_float(sf: torch.Tensor) -> torch.Tensor:
     dense.copy_(sf)
     b = dense.view(torch.uint8).to(torch.int32)
     return (b << 23).view(torch.float32)
+
+
+def per_channel_cast_fused(x, num_per_tokens: int, num_per_channels: Optional[int], round_sf: bool,
+                           pos_to_token: Optional[torch.Tensor]):
+    """Same contract as tile_kernels.torch.per_channel_cast_fused (per_channel_cast_fused.py:9-44): gather rows
+    through pos_to_token (negative = a row of zeros, data and scales), then the (128, 1)-block cast; FP8 input
+    carries one scale per (token, num_per_channels) that is multiplied in first."""
+    fused = isinstance(x, tuple)
+    if pos_to_token is not None:
+        idx = pos_to_token.clamp(min=0).long()
+        valid = (pos_to_token >= 0).unsqueeze(1)
+        data = x[0] if fused else x
+        gathered = torch.where(valid, data[idx].float(), torch.zeros(())).to(data.dtype)
+        x = (gathered, torch.where(valid, x[1][idx], torch.zeros(()))) if fused else gathered
+    return cast(x, 'e4m3', (num_per_tokens, 1), round_sf=round_sf, x_block_size=(1, num_per_channels) if fused else None)
 
 
 def cast_to_e5m6(x: torch.Tensor, num_per_channels: int, use_tma_aligned_col_major_sf: bool = False,

@@ -166,6 +166,50 @@ def gen_swiglu() -> None:
     np.savez_compressed(os.path.join(HERE, 'swiglu.npz'), **store)
 
 
+def gen_requant() -> None:
+    """Already quantized inputs (FP8 / FP4 data + scales in every layout) cast again per token, and the fused
+    per-channel cast with FP8 input and row gather (reference: tile_kernels/torch/cast.py:86-97,
+    tile_kernels/torch/per_channel_cast_fused.py:9-44)."""
+    from tile_kernels.torch.per_channel_cast_fused import per_channel_cast_fused
+    store = {}
+    g = torch.Generator().manual_seed(2468)
+    x = torch.randn((40, 256), generator=g).to(torch.bfloat16)
+    x[3] = 0
+    x[5] *= 300
+    put(store, 'x', x)
+    for in_fmt in ('e4m3', 'e2m1'):
+        for xbs in ((128, 128), (32, 32)):
+            for col, rnd, ue in ((False, True, False), (True, True, True)):
+                q, qsf = cast(x, in_fmt, xbs, round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+                key_in = f'{in_fmt}/{xbs[0]}/{int(col)}{int(rnd)}{int(ue)}'
+                put(store, key_in + '/q', q)
+                put(store, key_in + '/qsf', qsf)
+                for fmt in ('e4m3', 'e2m1'):
+                    for G in (32, 128):
+                        out, sf = cast((q, qsf), fmt, (1, G), x_block_size=xbs, round_sf=rnd, use_tma_aligned_col_major_sf=col,
+                                       use_packed_ue8m0=ue)
+                        put(store, f'{key_in}/{fmt}/g{G}/out', out)
+                        put(store, f'{key_in}/{fmt}/g{G}/sf', sf)
+    # fused per-channel cast: plain and FP8 + per-token-group scales, with and without gather
+    T, H = 128, 256
+    xb = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    q8, s8 = cast(xb, 'e4m3', (1, 128), round_sf=False)
+    pos = torch.randint(0, T, (144,), generator=g, dtype=torch.int32)
+    pos[::9] = -1
+    put(store, 'pc/x', xb)
+    put(store, 'pc/q8', q8)
+    put(store, 'pc/s8', s8)
+    put(store, 'pc/pos', pos)
+    for rnd in (False, True):
+        for src in ('bf16', 'fp8'):
+            for gather in (False, True):
+                xin = xb if src == 'bf16' else (q8, s8)
+                out, sf = per_channel_cast_fused(xin, 128, None if src == 'bf16' else 128, rnd, pos if gather else None)
+                put(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/out', out)
+                put(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/sf', sf)
+    np.savez_compressed(os.path.join(HERE, 'requant.npz'), **store)
+
+
 def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(raw(t).tobytes()).hexdigest()
 
@@ -198,6 +242,7 @@ if __name__ == '__main__':
     gen_e5m6()
     gen_e2m1_kat()
     gen_swiglu()
+    gen_requant()
     gen_config_digests()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

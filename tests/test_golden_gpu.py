@@ -139,3 +139,26 @@ def test_full_size_idempotent_scales(cuda_device):
     assert torch.equal(out1, out2)
     assert torch.equal(to_host(sf1), to_host(sf2)) and torch.equal(to_host(only), to_host(sf1))
     assert out1.dtype == torch.int8 and sf1.dtype == torch.int32 and sf1.shape == (8192, 56) and sf1.stride() == (1, 8192)
+
+
+@pytest.mark.parametrize('flags', [(False, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('xb', [128, 32])
+@pytest.mark.parametrize('in_fmt', ['e4m3', 'e2m1'])
+def test_requant_fixture(cuda_device, in_fmt, xb, flags):
+    """Already quantized inputs from the reference's fixtures, cast again on the GPU."""
+    from tilekernels_b200 import quant
+    store = golden('requant')
+    col, rnd, ue = flags
+    key_in = f'{in_fmt}/{xb}/{flags_id(flags)}'
+    q = golden_tensor(store, key_in + '/q').to(cuda_device)
+    qsf_host = golden_tensor(store, key_in + '/qsf')
+    # move the scales with their strides (column-major layouts are recognised by them)
+    span = 1 + sum((n - 1) * s for n, s in zip(qsf_host.shape, qsf_host.stride()))
+    qsf = torch.zeros(span, dtype=qsf_host.dtype, device=cuda_device).as_strided(qsf_host.shape, qsf_host.stride())
+    qsf.copy_(qsf_host)
+    for fmt in ('e4m3', 'e2m1'):
+        for G in (32, 128):
+            out, sf = quant.per_token_cast((q, qsf), fmt, G, x_block_size=(xb, xb), use_tma_aligned_col_major_sf=col,
+                                           round_sf=rnd, use_packed_ue8m0=ue)
+            assert_equal(to_host(out), golden_tensor(store, f'{key_in}/{fmt}/g{G}/out'))
+            assert_equal(to_host(sf), golden_tensor(store, f'{key_in}/{fmt}/g{G}/sf'))

@@ -60,8 +60,16 @@ def test_config_rules():
         common.get_cast_output_config('e4m3', (1, 128), use_packed_ue8m0=True)
     with pytest.raises(AssertionError):
         common.get_cast_input_and_config(torch.zeros(2, 2, dtype=torch.float16), None)
-    with pytest.raises(NotImplementedError):
-        common.get_cast_input_and_config((torch.zeros(2, 2, dtype=torch.int8), torch.zeros(2, 1)), (1, 32))
+    # already quantized inputs: the scale layout is recognised from strides and dtype
+    q = torch.zeros(8, 64, dtype=torch.int8)
+    _, sf, cfg = common.get_cast_input_and_config((q, torch.zeros(8, 4)), (1, 32))
+    assert cfg.with_sf and cfg.flags == 0 and sf.shape == (8, 4)
+    _, sf, cfg = common.get_cast_input_and_config((q, torch.zeros(4, 8).T), (1, 32))
+    assert cfg.flags == _lib.SF_COL_MAJOR and sf.shape == (4, 8)
+    _, sf, cfg = common.get_cast_input_and_config((q, torch.zeros(1, 8, dtype=torch.int32).T), (1, 32))
+    assert cfg.flags == _lib.SF_COL_MAJOR | _lib.SF_UE8M0 and sf.dtype == torch.uint8 and sf.shape == (1, 32)
+    with pytest.raises(AssertionError):
+        common.get_cast_input_and_config((torch.zeros(2, 2, dtype=torch.int32), torch.zeros(2, 1)), (1, 32))
     assert common.get_logical_hidden(64, torch.int8) == 128 and common.get_physical_hidden(128, torch.int8) == 64
 
 

@@ -139,6 +139,45 @@ def test_swiglu_cast_close_to_reference(oracle, with_w, clamp, G, flags):
     assert rel.numel() == 0 or rel.max().item() <= 1e-3
 
 
+def _requant_cases():
+    for in_fmt in ('e4m3', 'e2m1'):
+        for xb in (128, 32):
+            for flags in ((False, True, False), (True, True, True)):
+                for fmt in ('e4m3', 'e2m1'):
+                    for G in (32, 128):
+                        yield pytest.param(in_fmt, xb, flags, fmt, G, id=f'{in_fmt}-b{xb}-{flags_id(flags)}-{fmt}-g{G}')
+
+
+@pytest.mark.parametrize('in_fmt,xb,flags,fmt,G', list(_requant_cases()))
+def test_requant_matches_reference(oracle, in_fmt, xb, flags, fmt, G):
+    """Already quantized input (FP8 / FP4 + scales in each layout) cast again per token."""
+    store = golden('requant')
+    col, rnd, ue = flags
+    key_in = f'{in_fmt}/{xb}/{flags_id(flags)}'
+    q, qsf = golden_tensor(store, key_in + '/q'), golden_tensor(store, key_in + '/qsf')
+    # the first cast of the chain is an ordinary cast: check it too
+    x = golden_tensor(store, 'x')
+    q0, qsf0 = oracle.cast(x, in_fmt, (xb, xb), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+    assert_equal(q0, q)
+    assert_equal(qsf0, qsf)
+    out, sf = oracle.cast((q, qsf), fmt, (1, G), x_block_size=(xb, xb), round_sf=rnd, use_tma_aligned_col_major_sf=col,
+                          use_packed_ue8m0=ue)
+    assert_equal(out, golden_tensor(store, f'{key_in}/{fmt}/g{G}/out'))
+    assert_equal(sf, golden_tensor(store, f'{key_in}/{fmt}/g{G}/sf'))
+
+
+@pytest.mark.parametrize('gather', [False, True])
+@pytest.mark.parametrize('src', ['bf16', 'fp8'])
+@pytest.mark.parametrize('rnd', [False, True])
+def test_per_channel_cast_fused_matches_reference(oracle, rnd, src, gather):
+    store = golden('requant')
+    x = golden_tensor(store, 'pc/x') if src == 'bf16' else (golden_tensor(store, 'pc/q8'), golden_tensor(store, 'pc/s8'))
+    pos = golden_tensor(store, 'pc/pos') if gather else None
+    out, sf = oracle.per_channel_cast_fused(x, 128, None if src == 'bf16' else 128, rnd, pos)
+    assert_equal(out, golden_tensor(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/out'))
+    assert_equal(sf, golden_tensor(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/sf'))
+
+
 CONFIG_OPS = {
     'cfg1_per_token_e4m3_g128': ('cfg1', lambda o, x: o.cast(x, 'e4m3', (1, 128))),
     'cfg1_per_token_e4m3_g128_round': ('cfg1', lambda o, x: o.cast(x, 'e4m3', (1, 128), round_sf=True)),

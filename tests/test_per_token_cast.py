@@ -116,3 +116,35 @@ def test_misaligned_view_uses_narrow_loads(oracle, cuda_device):
     out_ref, sf_ref = oracle.cast(x_cpu, 'e4m3', (1, 128), round_sf=True)
     assert_equal(to_host(out), out_ref)
     assert_equal(to_host(sf), sf_ref)
+
+
+def _requant_params():
+    for num_tokens, hidden in ((4001, 576), (4001, 7168), (129, 2048), (33, 4096)):
+        for in_fmt in ('e4m3', 'e2m1'):
+            for xb in ((128, 128), (32, 32)):
+                for g in (32, 128):
+                    for fmt in ('e4m3', 'e2m1'):
+                        for flags in ((False, True, False), (True, True, True)):
+                            yield pytest.param(num_tokens, hidden, in_fmt, xb, g, fmt, flags,
+                                               id=f'{num_tokens}x{hidden}-{in_fmt}-b{xb[0]}-g{g}-{fmt}-{flags_id(flags)}')
+
+
+@pytest.mark.parametrize('num_tokens,hidden,in_fmt,xb,g,fmt,flags', list(_requant_params()))
+def test_per_token_cast_of_quantized_input(oracle, cuda_device, num_tokens, hidden, in_fmt, xb, g, fmt, flags):
+    """Already quantized input (reference test: tests/quant/test_per_token_cast.py:27-38,62-66: FP8 / FP4 data with
+    (128,128) or (32,32) block scales in the same layout as the requested output scales)."""
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    kw = dict(use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue)
+    x_cpu = make_input(num_tokens, hidden, torch.bfloat16)
+    q_ref, qsf_ref = oracle.cast(x_cpu, in_fmt, xb, **kw)
+    # quantize on the GPU as well, so that the scale tensor has the strides a real producer hands over
+    q, qsf = quant.per_block_cast(x_cpu.to(cuda_device), in_fmt, xb, **kw)
+    assert_equal(to_host(q), q_ref)
+    assert_equal(to_host(qsf), qsf_ref)
+    out, sf = quant.per_token_cast((q, qsf), fmt, g, x_block_size=xb, **kw)
+    out_ref, sf_ref = oracle.cast((q_ref, qsf_ref), fmt, (1, g), x_block_size=xb, **kw)
+    assert_equal(to_host(out), out_ref)
+    assert_equal(to_host(sf), sf_ref)
+    if rnd and not col and num_tokens > 1000:
+        check_bias(oracle.cast_back((out_ref, sf_ref), 'fp32', (1, g)), x_cpu.float())

@@ -5,9 +5,17 @@ hot path under the same names, argument lists and return conventions.  Every cal
 ends in one hand-written CUDA kernel of libtkquant.so (C ABI, see include/tkquant.h);
 there is no other backend and no CPU path: importing `quant` without the built
 library raises.
+
+Sub-modules load on first use, so that `python -m tilekernels_b200.build` can run before
+the library exists.
 """
-from . import config, utils  # noqa: F401
-from . import quant  # noqa: F401
-from . import testing  # noqa: F401
+import importlib
 
 __version__ = '0.1.0'
+_SUBMODULES = ('config', 'utils', 'quant', 'testing', 'host', 'sharding', 'build')
+
+
+def __getattr__(name):
+    if name in _SUBMODULES:
+        return importlib.import_module(f'{__name__}.{name}')
+    raise AttributeError(f'module {__name__!r} has no attribute {name!r}')

@@ -14,10 +14,10 @@ static int launch_group(const TokenCastParams& p, cudaStream_t stream) {
     // measured on B200: many resident warps with one step each beat fewer warps with several steps in flight;
     // FP4 (half the output bytes per step) prefers two
     const int u = group_unroll((DT == TKQ_DT_BF16 && FMT == TKQ_FMT_E2M1) ? 2 : 1, DT == TKQ_DT_BF16 ? 4 : 2);
-    if (u == 4) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, (DT == TKQ_DT_BF16 ? 4 : 2), 0>, p,
+    if (u == 4) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, (DT == TKQ_DT_BF16 ? 4 : 2), 0>, p,
                                            DT == TKQ_DT_BF16 ? 4 : 2, 0, stream, what);
-    if (u == 2) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, 2, 0>, p, 2, 0, stream, what);
-    return launch_group_kernel(group_cast_kernel<PlainSource<DT>, false, FMT, LPG, 1, 0>, p, 1, 0, stream, what);
+    if (u == 2) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, 2, 0>, p, 2, 0, stream, what);
+    return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, 1, 0>, p, 1, 0, stream, what);
 }
 
 template <int DT, int FMT>
@@ -105,6 +105,18 @@ int row_wait_flag() {
     if (cudaMemcpyFromSymbol(&v, g_row_wait_failed, sizeof(v)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(g_row_wait_failed, &zero, sizeof(zero));
     return static_cast<int>(v);
+}
+
+template <int QFMT, int FMT>
+static int dispatch_quant_group(const TokenCastParams& p, int64_t g, cudaStream_t stream) {
+    const char* what = "per_token_cast (quantized input)";
+    switch (g) {
+        case 16: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 1, 1, 0>, p, 1, 0, stream, what);
+        case 32: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 2, 1, 0>, p, 1, 0, stream, what);
+        case 64: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 4, 1, 0>, p, 1, 0, stream, what);
+        case 128: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 8, 1, 0>, p, 1, 0, stream, what);
+    }
+    return set_error(TKQ_E_UNSUPPORTED, "per_token_cast (quantized input): num_per_channels must be 16, 32, 64 or 128");
 }
 
 static int check_sf_flags(unsigned flags, const void* sf, int64_t sf_stride, const char** why) {
@@ -217,4 +229,55 @@ extern "C" int tkq_per_token_cast_e5m6(const void* x, int in_dtype, int64_t num_
     p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 65024.0f);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return in_dtype == TKQ_DT_BF16 ? dispatch_e5m6<TKQ_DT_BF16>(p, s) : dispatch_e5m6<TKQ_DT_FP32>(p, s);
+}
+
+extern "C" int tkq_per_token_cast_quantized(const void* x, int in_fmt, const void* x_sf, unsigned x_sf_flags, int64_t x_sf_stride,
+                                            int x_block_m, int x_block_k, int64_t num_tokens, int64_t hidden,
+                                            int64_t x_row_stride, int fmt, int64_t num_per_channels, unsigned flags, void* out,
+                                            void* sf, int64_t sf_stride, void* stream) {
+    if (num_tokens < 0 || hidden <= 0 || x_row_stride < hidden || (in_fmt != TKQ_FMT_E4M3 && in_fmt != TKQ_FMT_E2M1) ||
+        (fmt != TKQ_FMT_E4M3 && fmt != TKQ_FMT_E2M1) || x_block_m <= 0 || x_block_k <= 0)
+        return set_error(TKQ_E_BAD_ARG, "per_token_cast (quantized input): bad size or format");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || x_sf == nullptr || sf == nullptr || out == nullptr)
+        return set_error(TKQ_E_BAD_ARG, "per_token_cast (quantized input): null pointer");
+    if (flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY))
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast (quantized input): sf-only / cast-only are not defined");
+    if ((x_sf_flags & TKQ_SF_UE8M0) && !(x_sf_flags & TKQ_SF_COL_MAJOR))
+        return set_error(TKQ_E_UNSUPPORTED, "packed ue8m0 input scales need the column-major layout");
+    const char* why = "";
+    if (int rc = check_sf_flags(flags, sf, sf_stride, &why)) return set_error(rc, why);
+    // a lane's 16 values must share one input scale and one 16-byte (FP8) or 8-byte (FP4) load
+    if (hidden % 16 != 0 || x_block_k % 16 != 0)
+        return set_error(TKQ_E_UNSUPPORTED, "per_token_cast (quantized input): hidden and the input block width must be multiples of 16");
+    const int64_t row_bytes = in_fmt == TKQ_FMT_E4M3 ? x_row_stride : x_row_stride / 2;
+    const int align = in_fmt == TKQ_FMT_E4M3 ? 16 : 8;
+    if (reinterpret_cast<uintptr_t>(x) % align != 0 || row_bytes % align != 0 || !aligned16(out) ||
+        (reinterpret_cast<uintptr_t>(x_sf) & 3u) != 0)
+        return set_error(TKQ_E_ALIGNMENT, "per_token_cast (quantized input): x rows must be 16-byte (FP8) or 8-byte (FP4) aligned");
+
+    TokenCastParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = sf;
+    p.x_stride = x_row_stride;
+    p.sf_stride = sf_stride;
+    p.out_stride = fmt == TKQ_FMT_E4M3 ? hidden : hidden / 2;
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.flags = flags;
+    p.clamp_min = fmt == TKQ_FMT_E4M3 ? 1e-4f : 6.0f * 1.1754943508222875e-38f;
+    p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, fmt == TKQ_FMT_E4M3 ? 448.0f : 6.0f);
+    p.num_groups = static_cast<uint32_t>((hidden + num_per_channels - 1) / num_per_channels);
+    p.in_sf = x_sf;
+    p.in_sf_stride = x_sf_stride;
+    p.in_sf_flags = x_sf_flags;
+    p.in_block_m = static_cast<uint32_t>(x_block_m);
+    p.in_block_k = static_cast<uint32_t>(x_block_k);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in_fmt == TKQ_FMT_E4M3)
+        return fmt == TKQ_FMT_E4M3 ? dispatch_quant_group<TKQ_FMT_E4M3, TKQ_FMT_E4M3>(p, num_per_channels, s)
+                                   : dispatch_quant_group<TKQ_FMT_E4M3, TKQ_FMT_E2M1>(p, num_per_channels, s);
+    return fmt == TKQ_FMT_E4M3 ? dispatch_quant_group<TKQ_FMT_E2M1, TKQ_FMT_E4M3>(p, num_per_channels, s)
+                               : dispatch_quant_group<TKQ_FMT_E2M1, TKQ_FMT_E2M1>(p, num_per_channels, s);
 }

@@ -20,6 +20,7 @@ struct PlainSource;
 template <>
 struct PlainSource<TKQ_DT_BF16> {
     static constexpr int kElemBytes = 2;
+    __host__ __device__ static constexpr int64_t bytes(int64_t elems) { return elems * 2; }
     struct Raw {
         U32x8 a;
     };
@@ -52,6 +53,7 @@ struct PlainSource<TKQ_DT_BF16> {
 template <>
 struct PlainSource<TKQ_DT_FP32> {
     static constexpr int kElemBytes = 4;
+    __host__ __device__ static constexpr int64_t bytes(int64_t elems) { return elems * 4; }
     struct Raw {
         U32x8 a, b;
     };
@@ -94,6 +96,7 @@ template <int DT>
 struct SwigluSource {
     using P = PlainSource<DT>;
     static constexpr int kElemBytes = P::kElemBytes;
+    __host__ __device__ static constexpr int64_t bytes(int64_t elems) { return elems * kElemBytes; }
     struct Raw {
         typename P::Raw g, u;
     };
@@ -130,6 +133,61 @@ struct SwigluSource {
         if (kWeight && w != 1.0f) {  // uniform over the row; multiplying by exactly 1 would change nothing
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], w);
+        }
+    }
+};
+
+// Already quantized input (reference: the with_sf branch of tile_kernels/quant/per_token_cast_kernel.py:87-126
+// and tile_kernels/torch/cast.py:86-97): FP8 e4m3 bytes or packed FP4 e2m1 nibbles plus one scale per input
+// block.  A lane's 16 values lie in one input block (blocks are at least 32 wide), so unpack() takes the one
+// scale and returns float(x) * scale, the fp32 product the reference forms before it takes the maximum.
+template <int QFMT>
+struct QuantSource;
+
+template <>
+struct QuantSource<TKQ_FMT_E4M3> {
+    __host__ __device__ static constexpr int64_t bytes(int64_t elems) { return elems; }
+    struct Raw {
+        U32x4 a;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) { r.a.v[0] = r.a.v[1] = r.a.v[2] = r.a.v[3] = 0; }
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool) { r.a = ldg128(p); }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v, float scale) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint16_t pair = static_cast<uint16_t>(r.a.v[i] >> (16 * h));
+                uint32_t f16x2;
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(f16x2) : "h"(pair));
+                const __half2 hv = *reinterpret_cast<const __half2*>(&f16x2);
+                v[4 * i + 2 * h] = __fmul_rn(__low2float(hv), scale);
+                v[4 * i + 2 * h + 1] = __fmul_rn(__high2float(hv), scale);
+            }
+        }
+    }
+};
+
+template <>
+struct QuantSource<TKQ_FMT_E2M1> {
+    __host__ __device__ static constexpr int64_t bytes(int64_t elems) { return elems / 2; }
+    struct Raw {
+        uint32_t lo, hi;
+    };
+    __device__ __forceinline__ static void zero(Raw& r) { r.lo = r.hi = 0; }
+    __device__ __forceinline__ static void issue(Raw& r, const void* p, bool) {
+        asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(r.lo), "=r"(r.hi) : "l"(p));
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v, float scale) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t word = i < 4 ? r.lo : r.hi;
+            const uint16_t byte = static_cast<uint16_t>((word >> (8 * (i & 3))) & 0xFFu);  // two codes, even index low
+            uint32_t f16x2;
+            asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(f16x2) : "h"(byte));
+            const __half2 hv = *reinterpret_cast<const __half2*>(&f16x2);
+            v[2 * i] = __fmul_rn(__low2float(hv), scale);
+            v[2 * i + 1] = __fmul_rn(__high2float(hv), scale);
         }
     }
 };

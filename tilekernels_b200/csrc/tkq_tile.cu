@@ -351,6 +351,102 @@ static int dispatch_block(const TileParams& p, int bm, int bk, cudaStream_t s) {
     return set_error(TKQ_E_UNSUPPORTED, "per_block_cast: block sizes must be 32 or 128");
 }
 
+// ---------------------------------------------------------------------------
+// Fused per-channel cast: the per-channel cast of rows gathered through `pos_to_token` (a negative entry gives a
+// row of zeros) and/or of FP8 input with one fp32 scale per (token, 128 channels), which is multiplied in before
+// the maximum is taken (reference: tile_kernels/quant/per_channel_cast_fused_kernel.py:50-132,
+// tile_kernels/torch/per_channel_cast_fused.py:9-44).  Gathered rows are not a rectangle, so this kernel reads
+// its 128 x 128 tile with plain vector loads, one block per tile; the arithmetic is that of
+// per_channel_cast_kernel.
+// ---------------------------------------------------------------------------
+constexpr int kInFp8 = 2;  // input kind next to TKQ_DT_BF16 / TKQ_DT_FP32
+
+struct FusedChannelParams {
+    const void* x;
+    const float* x_sf;           // [num_tokens_in, hidden / 128], FP8 input only
+    const int32_t* pos_to_token;  // [num_tokens_out] or null
+    uint8_t* out;
+    float* sf;
+    int64_t num_tokens_in, num_tokens_out, hidden;
+    uint32_t tiles_k;
+    uint32_t flags;
+    float clamp_min;
+    bool fast_pow2;
+    bool wide_loads;
+};
+
+template <int IN>
+__global__ void __launch_bounds__(kTileThreads) per_channel_cast_fused_kernel(const FusedChannelParams p) {
+    __shared__ int col_amax_bits[kTile];
+    __shared__ float col_inv[kTile];
+    const int t = threadIdx.x, lane = t & 31;
+    const int c16 = t & 7, r_base = t >> 3;
+    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
+    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
+    const int valid_rows = static_cast<int>(p.num_tokens_out - row0 < kTile ? p.num_tokens_out - row0 : kTile);
+    const int valid_cols = static_cast<int>(p.hidden - col0 < kTile ? p.hidden - col0 : kTile);
+    const bool col_ok = c16 * 16 < valid_cols;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    if (t < kTile) col_amax_bits[t] = 0;
+
+    float v[4][16];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = r_base + 32 * k;
+        int64_t src_row = -1;
+        if (col_ok && r < valid_rows) src_row = p.pos_to_token != nullptr ? p.pos_to_token[row0 + r] : row0 + r;
+        if (src_row >= 0) {
+            const int64_t elem = src_row * p.hidden + col0 + c16 * 16;
+            if constexpr (IN == kInFp8) {
+                typename QuantSource<TKQ_FMT_E4M3>::Raw raw;
+                QuantSource<TKQ_FMT_E4M3>::issue(raw, static_cast<const uint8_t*>(p.x) + elem, false);
+                QuantSource<TKQ_FMT_E4M3>::unpack(raw, v[k], p.x_sf[src_row * (p.hidden / 128) + (col0 + c16 * 16) / 128]);
+            } else {
+                typename PlainSource<IN>::Raw raw;
+                PlainSource<IN>::issue(raw, static_cast<const uint8_t*>(p.x) + PlainSource<IN>::bytes(elem), p.wide_loads);
+                PlainSource<IN>::unpack(raw, v[k]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[k][j] = 0.0f;
+        }
+    }
+    float cm[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        cm[j] = max3_abs(fabsf(v[0][j]), v[1][j], max3_abs(0.0f, v[2][j], v[3][j]));
+        cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 8));
+        cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 16));
+    }
+    __syncthreads();  // col_amax_bits is cleared
+    if (lane < 8) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) atomicMax(&col_amax_bits[c16 * 16 + j], __float_as_int(cm[j]));
+    }
+    __syncthreads();
+    if (t < kTile) {
+        const Scale s = make_scale_for<TKQ_FMT_E4M3>(__int_as_float(col_amax_bits[t]), p.clamp_min, round_sf, p.fast_pow2);
+        col_inv[t] = s.inv;
+        if (t < valid_cols) p.sf[tile_m * p.hidden + col0 + t] = s.sf;
+    }
+    __syncthreads();
+    float inv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) inv[j] = col_inv[c16 * 16 + j];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = r_base + 32 * k;
+        if (col_ok && r < valid_rows) {
+            float q[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) q[j] = __fmul_rn(v[k][j], inv[j]);
+            stg128(p.out + (row0 + r) * p.hidden + col0 + c16 * 16, cvt_e4m3x4(q[0], q[1], q[2], q[3]),
+                   cvt_e4m3x4(q[4], q[5], q[6], q[7]), cvt_e4m3x4(q[8], q[9], q[10], q[11]),
+                   cvt_e4m3x4(q[12], q[13], q[14], q[15]));
+        }
+    }
+}
+
 }  // namespace tkq
 
 using namespace tkq;
@@ -430,4 +526,45 @@ extern "C" int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tok
     return in_dtype == TKQ_DT_BF16
                ? launch_tile(per_channel_cast_kernel<TKQ_DT_BF16>, p, 2, "per_channel_cast", s)
                : launch_tile(per_channel_cast_kernel<TKQ_DT_FP32>, p, 4, "per_channel_cast", s);
+}
+
+extern "C" int tkq_per_channel_cast_fused(const void* x, int in_kind, const float* x_sf, const int32_t* pos_to_token,
+                                          int64_t num_tokens_in, int64_t num_tokens_out, int64_t hidden, unsigned flags,
+                                          void* out, void* sf, void* stream) {
+    if (num_tokens_in < 0 || num_tokens_out < 0 || hidden <= 0 ||
+        (in_kind != TKQ_DT_BF16 && in_kind != TKQ_DT_FP32 && in_kind != kInFp8))
+        return set_error(TKQ_E_BAD_ARG, "per_channel_cast_fused: bad size or input kind");
+    if (num_tokens_out == 0) return 0;
+    if (x == nullptr || sf == nullptr || out == nullptr || (in_kind == kInFp8) != (x_sf != nullptr))
+        return set_error(TKQ_E_BAD_ARG, "per_channel_cast_fused: null pointer (input scales go with FP8 input, and only with it)");
+    if (flags & ~TKQ_ROUND_SF) return set_error(TKQ_E_UNSUPPORTED, "per_channel_cast_fused: only TKQ_ROUND_SF is defined");
+    if (hidden % 64 != 0 || (in_kind == kInFp8 && hidden % 128 != 0))
+        return set_error(TKQ_E_UNSUPPORTED, "per_channel_cast_fused: hidden % 64 == 0 (128 for FP8 input) required");
+    if (num_tokens_out % (pos_to_token != nullptr ? 16 : 128) != 0)
+        return set_error(TKQ_E_UNSUPPORTED, "per_channel_cast_fused: output tokens must be a multiple of 128 (16 with pos_to_token)");
+    if (!aligned16(x) || !aligned16(out) || (reinterpret_cast<uintptr_t>(sf) & 3u))
+        return set_error(TKQ_E_ALIGNMENT, "per_channel_cast_fused: x and out must be 16-byte aligned, sf 4-byte aligned");
+    FusedChannelParams p{};
+    p.x = x;
+    p.x_sf = x_sf;
+    p.pos_to_token = pos_to_token;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = static_cast<float*>(sf);
+    p.num_tokens_in = num_tokens_in;
+    p.num_tokens_out = num_tokens_out;
+    p.hidden = hidden;
+    p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
+    p.flags = flags;
+    p.clamp_min = 1e-4f;
+    p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
+    const int elem = in_kind == TKQ_DT_BF16 ? 2 : 4;
+    p.wide_loads = in_kind != kInFp8 && reinterpret_cast<uintptr_t>(x) % 32 == 0 && (hidden * elem) % 32 == 0;
+    const int64_t tiles = ((num_tokens_out + kTile - 1) / kTile) * p.tiles_k;
+    if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>(tiles);
+    if (in_kind == TKQ_DT_BF16) per_channel_cast_fused_kernel<TKQ_DT_BF16><<<grid, kTileThreads, 0, s>>>(p);
+    else if (in_kind == TKQ_DT_FP32) per_channel_cast_fused_kernel<TKQ_DT_FP32><<<grid, kTileThreads, 0, s>>>(p);
+    else per_channel_cast_fused_kernel<kInFp8><<<grid, kTileThreads, 0, s>>>(p);
+    return check_launch("per_channel_cast_fused");
 }

@@ -42,7 +42,26 @@ struct TokenCastParams {
     const int32_t* pos_to_expert;
     float swiglu_clamp;
     unsigned long long* clamped_count;
+    // already quantized input only: its scales (layouts as for the output scales) and their block shape
+    const void* in_sf;
+    int64_t in_sf_stride;
+    uint32_t in_sf_flags;  // TKQ_SF_COL_MAJOR, TKQ_SF_UE8M0
+    uint32_t in_block_m, in_block_k;
 };
+
+constexpr int kSourcePlain = 0, kSourceSwiglu = 1, kSourceQuant = 2;
+
+// The input scale that applies to (row, col) of an already quantized input
+// (reference: tile_kernels/quant/common.py:219-235 load_sf + transform_sf).
+__device__ __forceinline__ float load_input_scale(const TokenCastParams& p, uint32_t row, uint32_t col) {
+    const int64_t m = row / p.in_block_m, k = col / p.in_block_k;
+    if (p.in_sf_flags & TKQ_SF_UE8M0) {
+        const uint8_t e = static_cast<const uint8_t*>(p.in_sf)[(k >> 2) * p.in_sf_stride + 4 * m + (k & 3)];
+        return __uint_as_float(static_cast<uint32_t>(e) << 23);
+    }
+    const float* f = static_cast<const float*>(p.in_sf);
+    return (p.in_sf_flags & TKQ_SF_COL_MAJOR) ? f[k * p.in_sf_stride + m] : f[m * p.in_sf_stride + k];
+}
 
 constexpr int kGroupThreads = 256;
 
@@ -62,8 +81,10 @@ __device__ __forceinline__ void flush_clamp_counters(const ClampCounters& cnt, u
 }
 
 // kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count (SwiGLU sources only)
-template <class Src, bool kSwiglu, int FMT, int LPG, int U, int kClampMode>
+template <class Src, int kKind, int FMT, int LPG, int U, int kClampMode>
 __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCastParams p) {
+    constexpr bool kSwiglu = kKind == kSourceSwiglu;
+    constexpr bool kQuant = kKind == kSourceQuant;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -92,12 +113,12 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
         if (kSwiglu && p.pos_to_expert != nullptr && p.pos_to_expert[this_row] < 0) continue;  // warp-uniform
 
         typename Src::Raw raw[U];
-        const uint8_t* src = xb + (static_cast<int64_t>(this_row) * p.x_stride + col0) * Src::kElemBytes;
+        const uint8_t* src = xb + Src::bytes(static_cast<int64_t>(this_row) * p.x_stride + col0);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (col0 + u * 512u < hidden) {
-                if constexpr (kSwiglu) Src::issue(raw[u], src + u * 512 * Src::kElemBytes, wide, p.hidden);
-                else Src::issue(raw[u], src + u * 512 * Src::kElemBytes, wide);
+                if constexpr (kSwiglu) Src::issue(raw[u], src + Src::bytes(u * 512), wide, p.hidden);
+                else Src::issue(raw[u], src + Src::bytes(u * 512), wide);
             } else {
                 Src::zero(raw[u]);
             }
@@ -116,6 +137,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
             if (U > 1 && col - lane * 16u >= hidden) break;  // warp-uniform: the whole step lies beyond the row
             float v[16];
             if constexpr (kSwiglu) Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt);
+            else if constexpr (kQuant) Src::unpack(raw[u], v, col < hidden ? load_input_scale(p, this_row, col) : 0.0f);
             else Src::unpack(raw[u], v);
             const bool in_row = col < hidden;
             const uint32_t g = col / (16u * LPG);
@@ -204,7 +226,7 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_kernel(const TokenCas
         for (int k = 0; k < K; ++k) {
             const int64_t col = (static_cast<int64_t>(threadIdx.x) + k * blockDim.x) * 16;
             if (col < p.hidden) {
-                const uint8_t* src = xb + (row * p.x_stride + col) * Src::kElemBytes;
+                const uint8_t* src = xb + Src::bytes(row * p.x_stride + col);
                 if constexpr (kSwiglu) Src::issue(raw[k], src, wide, p.hidden);
                 else Src::issue(raw[k], src, wide);
             } else {

@@ -6,7 +6,7 @@ scale-factor shapes, allocation and epilogue (:130-193) and the FP4 unpacker
 (:247-295).  The device-side macros of that file (get_sf_and_inv, load_sf,
 store_sf) live in csrc/tkq_common.cuh.
 """
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Optional, Union
 
 import torch
@@ -35,6 +35,11 @@ class BaseCastConfig:
 @dataclass(frozen=True)
 class CastInputConfig(BaseCastConfig):
     with_sf: bool = True
+
+    @property
+    def flags(self) -> int:
+        """Layout bits of include/tkquant.h for the scales of an already quantized input."""
+        return (_lib.SF_COL_MAJOR if self.use_tma_aligned_col_major_sf else 0) | (_lib.SF_UE8M0 if self.use_packed_ue8m0 else 0)
 
 
 @dataclass(frozen=True)
@@ -69,10 +74,26 @@ def get_cast_input_and_config(
     x: Union[torch.Tensor, QuantTensor],
     sf_block: Optional[tuple[int, int]],
 ) -> tuple[torch.Tensor, Optional[torch.Tensor], CastInputConfig]:
+    """Normalise the input of a cast.  A plain tensor must be bfloat16 / float32.  A `(data, scales)` pair is an
+    already quantized tensor: its scale layout is recognised from strides and dtype (unit stride along tokens =
+    column-major; int32 = packed ue8m0) and the scales come back as their row-major *storage* (a transposed view,
+    bytes for the packed layout), as in the reference (tile_kernels/quant/common.py:62-88)."""
     if isinstance(x, tuple):
-        raise NotImplementedError(
-            'QuantTensor (already quantized) inputs are not implemented in tilekernels_b200 yet; '
-            'pass a bfloat16 or float32 tensor')
+        assert isinstance(sf_block, tuple)
+        x, x_sf = x
+        config = CastInputConfig(torch_dtype=x.dtype, with_sf=True, sf_block=tuple(sf_block))
+        assert isinstance(x, torch.Tensor) and isinstance(x_sf, torch.Tensor)
+        assert x.dtype in (torch.float8_e4m3fn, torch.int8, torch.uint8)
+        if x_sf.stride(0) == 1:
+            config = replace(config, use_tma_aligned_col_major_sf=True)
+            x_sf = x_sf.T
+            if x_sf.dtype == torch.int32:
+                config = replace(config, use_packed_ue8m0=True)
+                x_sf = x_sf.view(torch.uint8)
+        else:
+            assert x_sf.stride(1) == 1
+            assert x_sf.dtype == torch.float32
+        return x, x_sf, config
     assert sf_block is None
     assert isinstance(x, torch.Tensor)
     assert x.dtype in (torch.bfloat16, torch.float32)

@@ -28,7 +28,7 @@ def per_token_cast_impl(
         assert sf is None
         return per_token_cast_to_e5m6(x, num_per_channels, use_tma_aligned_col_major_sf, round_sf, use_packed_ue8m0)
 
-    x, _, in_config = get_cast_input_and_config(x, x_block_size)
+    x, x_sf, in_config = get_cast_input_and_config(x, x_block_size)
     out_config = get_cast_output_config(fmt, (1, num_per_channels), use_tma_aligned_col_major_sf, round_sf, use_packed_ue8m0)
 
     assert x.dim() == 2 and x.is_cuda and (x.shape[1] == 0 or x.stride(1) == 1)
@@ -37,6 +37,10 @@ def per_token_cast_impl(
     assert num_per_channels in (16, 32, 64, 128) or (num_per_channels == hidden and hidden % 64 == 0)
     if num_per_channels == hidden and num_per_channels not in (16, 32, 64, 128):
         assert not sf_only and sf is None  # one scale per token has no sf-only / cast-only form
+        assert not in_config.with_sf
+    if in_config.with_sf:
+        assert not sf_only and sf is None
+        assert num_per_channels in (16, 32, 64, 128) and in_config.sf_block[1] % 16 == 0
 
     flags = out_config.flags
     if sf_only:
@@ -52,10 +56,18 @@ def per_token_cast_impl(
     out_sf = sf if sf is not None else alloc_scaling_factors((num_tokens, hidden), out_config=out_config, device=x.device)
     if num_tokens > 0:
         with torch.cuda.device(x.device):
-            rc = _lib.lib().tkq_per_token_cast(
-                x.data_ptr(), DTYPE_TO_ENUM[x.dtype], num_tokens, hidden, x.stride(0), FMT_TO_ENUM[fmt], num_per_channels,
-                flags, out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))
-        _lib.check(rc, 'tkq_per_token_cast')
+            if in_config.with_sf:
+                rc = _lib.lib().tkq_per_token_cast_quantized(
+                    x.data_ptr(), _lib.FMT_E4M3 if x.dtype == torch.float8_e4m3fn else _lib.FMT_E2M1, x_sf.data_ptr(),
+                    in_config.flags, x_sf.stride(0), in_config.sf_block[0], in_config.sf_block[1], num_tokens, hidden,
+                    get_logical_hidden(x.stride(0), x.dtype), FMT_TO_ENUM[fmt], num_per_channels, flags, out.data_ptr(),
+                    out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))
+                _lib.check(rc, 'tkq_per_token_cast_quantized')
+            else:
+                rc = _lib.lib().tkq_per_token_cast(
+                    x.data_ptr(), DTYPE_TO_ENUM[x.dtype], num_tokens, hidden, x.stride(0), FMT_TO_ENUM[fmt], num_per_channels,
+                    flags, out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))
+                _lib.check(rc, 'tkq_per_token_cast')
 
     out_sf = cast_epilogue(out_sf, num_tokens, hidden, out_config)
     if sf_only:
@@ -77,10 +89,11 @@ def per_token_cast(
     """Cast a matrix to FP8 / FP4 / E5M6 with one scale per (1 x num_per_channels) group of a token.
 
     Args:
-        x: 2-D CUDA tensor (num_tokens, hidden), bfloat16 or float32; rows may be strided.
+        x: 2-D CUDA tensor (num_tokens, hidden), bfloat16 or float32, rows may be strided; or an already
+            quantized pair (data, scales) with data float8_e4m3fn or int8 (two FP4 per byte).
         fmt: 'e4m3', 'e2m1' or 'e5m6'.
         num_per_channels: 16, 32, 64, 128 or hidden ('e5m6': hidden).
-        x_block_size: scale block of an already quantized input (not implemented here).
+        x_block_size: scale block (rows, channels) of an already quantized input, e.g. (128, 128) or (32, 32).
         use_tma_aligned_col_major_sf: column-major scales, token dimension padded to 16 bytes.
         round_sf: round scales up to powers of two.
         use_packed_ue8m0: store scales as exponent bytes, four per int32.
