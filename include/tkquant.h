@@ -163,6 +163,21 @@ int tkq_per_channel_cast_fused(const void* x, int in_kind, const float* x_sf, co
                                void* sf, void* stream);
 
 /*
+ * Dequantise: out = float(x) * scale of the value's block, formed in fp32 and rounded once to bf16 or fp32.
+ * Replaces the launches in tile_kernels/quant/cast_back_kernel.py:118-119 (cast_back, per_token_cast_back;
+ * kernel :51-72) and tile_kernels/quant/cast_back_e5m6_kernel.py (cast_back_e5m6).
+ *
+ *   x          in_fmt e4m3: [num_tokens, hidden] bytes; e2m1: [num_tokens, hidden / 2] bytes;
+ *              e5m6: [num_tokens, hidden / 8 * 3] uint32 words; contiguous
+ *   x_sf       scales, m = token / x_block_m, k = channel / x_block_k, layout given by x_sf_flags
+ *              (0 = row-major fp32, TKQ_SF_COL_MAJOR, TKQ_SF_COL_MAJOR | TKQ_SF_UE8M0), x_sf_stride as sf_stride above
+ *   out_dtype  TKQ_DT_BF16 or TKQ_DT_FP32;  out  [num_tokens, hidden], contiguous
+ * hidden and x_block_k must be multiples of 16.
+ */
+int tkq_cast_back(const void* x, int in_fmt, const void* x_sf, unsigned x_sf_flags, int64_t x_sf_stride, int x_block_m,
+                  int x_block_k, int64_t num_tokens, int64_t hidden, int out_dtype, void* out, void* stream);
+
+/*
  * Fused SwiGLU + per-token e4m3 cast: y = silu(x[:, :hidden]) * x[:, hidden:] in fp32
  * (times an optional per-row weight), then the per-token cast of y.
  * Replaces the launch in tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:255-256

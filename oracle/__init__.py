@@ -133,6 +133,22 @@ def cast_back(x, fmt: str, block_size=(32, 32)) -> torch.Tensor:
     return out if fmt == 'fp32' else out.bfloat16()
 
 
+def cast_back_from_e5m6(x, fmt: str, x_block_size) -> torch.Tensor:
+    """Dequantise packed E5M6 (tile_kernels/torch/cast_e5m6.py:221-258)."""
+    data, sf = x
+    assert data.dtype == torch.uint8
+    T = data.shape[0]
+    H = data.shape[1] * 2 // 3
+    bm, bk = x_block_size
+    sf32 = sf_to_float(sf)[:, :_ceil_div(H, bk)].contiguous()
+    out = torch.empty((T, H), dtype=torch.float32)
+    if T > 0:
+        rc = lib().tkqo_cast_back_e5m6(_vp(data.contiguous().data_ptr()), _i64(T), _i64(H), int(bm), int(bk), _vp(sf32.data_ptr()),
+                                       _vp(out.data_ptr()))
+        assert rc == 0
+    return out if fmt == 'fp32' else out.bfloat16()
+
+
 def sf_to_float(sf: torch.Tensor) -> torch.Tensor:
     """fp32 scales unchanged; packed int32 ue8m0 words -> fp32 [nm, 4*words] (cast.py:28-37)."""
     if sf.dtype == torch.float32:

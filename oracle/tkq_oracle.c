@@ -259,6 +259,34 @@ int tkqo_cast_e5m6(const void* x, int in_dtype, int64_t T, int64_t H, int64_t x_
     return 0;
 }
 
+/*
+ * tkqo_cast_back_e5m6 (cast_e5m6.py:103-132, 221-258): words -> 12-bit codes -> fp16 (code << 4) -> fp32,
+ * times the row-major fp32 scale of the value's (bm x bk) block.
+ */
+static inline float f16_bits_to_f32(uint32_t h) {
+    uint32_t sign = (h & 0x8000u) << 16, e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
+    if (e == 0) return u2f(sign) + (sign ? -1.0f : 1.0f) * ldexpf((float)m, -24) * (m != 0);
+    if (e == 31) return u2f(sign | 0x7F800000u | (m << 13));
+    return u2f(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+int tkqo_cast_back_e5m6(const uint32_t* words, int64_t T, int64_t H, int bm, int bk, const float* sf, float* out_fp32) {
+    if (H % 8) return -1;
+    const int64_t nbk = (H + bk - 1) / bk;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < T; ++r)
+        for (int64_t o = 0; o < H / 8; ++o) {
+            const uint32_t* w = words + r * (H / 8 * 3) + o * 3;
+            uint32_t h[8] = {w[0] >> 16, w[0] >> 4, (w[0] << 8) | (w[1] >> 24), w[1] >> 12, w[1], (w[1] << 12) | (w[2] >> 20),
+                             w[2] >> 8, w[2] << 4};
+            for (int i = 0; i < 8; ++i) {
+                int64_t c = o * 8 + i;
+                out_fp32[r * H + c] = f16_bits_to_f32(h[i] & 0xFFF0u) * sf[(r / bm) * nbk + c / bk];
+            }
+        }
+    return 0;
+}
+
 /* ---- exp(x), fp32, built from IEEE add/mul/fma and integer operations only, so that the CUDA copy
  * (csrc/tkq_common.cuh, tkq_expf) produces the same bits.  The argument is clamped to [-87, 88] (the
  * result stays a normal number; callers only use 1 + exp(x), for which the clamp changes nothing

@@ -210,6 +210,33 @@ def gen_requant() -> None:
     np.savez_compressed(os.path.join(HERE, 'requant.npz'), **store)
 
 
+def gen_cast_back() -> None:
+    """Dequantisation (reference: tile_kernels/torch/cast.py:40-59, cast_e5m6.py:221-258).  Only the fp32 result is
+    stored; the bf16 result is by definition that tensor rounded to bfloat16."""
+    from tile_kernels.torch import cast_back_from_e5m6
+    store = {}
+    g = torch.Generator().manual_seed(1357)
+    x = torch.randn((40, 128), generator=g).to(torch.bfloat16)
+    x[2] = 0
+    x[7] *= 1000
+    put(store, 'x', x)
+    for fmt in ('e4m3', 'e2m1'):
+        for bs in ((1, 32), (1, 128), (128, 128), (32, 32)):
+            for col, rnd, ue in ((False, True, False), (True, True, True)):
+                q, qsf = cast(x, fmt, bs, round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+                key = f'{fmt}/{bs[0]}x{bs[1]}/{int(col)}{int(rnd)}{int(ue)}'
+                put(store, key + '/q', q)
+                put(store, key + '/qsf', qsf)
+                put(store, key + '/back', cast_back((q, qsf), 'fp32', bs))
+    for col, rnd, ue in FLAG_SETS:
+        q, qsf = cast_to_e5m6(x, 128, col, rnd, ue)
+        key = f'e5m6/{int(col)}{int(rnd)}{int(ue)}'
+        put(store, key + '/q', q)
+        put(store, key + '/qsf', qsf)
+        put(store, key + '/back', cast_back_from_e5m6((q, qsf), 'fp32', (1, 128)))
+    np.savez_compressed(os.path.join(HERE, 'cast_back.npz'), **store)
+
+
 def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(raw(t).tobytes()).hexdigest()
 
@@ -243,6 +270,7 @@ if __name__ == '__main__':
     gen_e2m1_kat()
     gen_swiglu()
     gen_requant()
+    gen_cast_back()
     gen_config_digests()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
