@@ -178,6 +178,18 @@ int tkq_cast_back(const void* x, int in_fmt, const void* x_sf, unsigned x_sf_fla
                   int x_block_k, int64_t num_tokens, int64_t hidden, int out_dtype, void* out, void* stream);
 
 /*
+ * Per-channel cast to e4m3 with transposed output: one scale per (num_per_tokens tokens x 1 channel),
+ * num_per_tokens = 32 or 128; data written as [hidden, num_tokens].
+ * Replaces the launch in tile_kernels/quant/per_channel_cast_and_transpose_kernel.py:120-121 (kernel :30-82).
+ *
+ *   x      [num_tokens, hidden] bf16, contiguous, num_tokens % 128 == 0, hidden % 64 == 0
+ *   out    [hidden, num_tokens] bytes;  sf  [num_tokens / num_per_tokens, hidden] fp32
+ * flags: TKQ_ROUND_SF only.
+ */
+int tkq_per_channel_cast_and_transpose(const void* x, int64_t num_tokens, int64_t hidden, int num_per_tokens, unsigned flags,
+                                       void* out, void* sf, void* stream);
+
+/*
  * Fused SwiGLU + per-token e4m3 cast: y = silu(x[:, :hidden]) * x[:, hidden:] in fp32
  * (times an optional per-row weight), then the per-token cast of y.
  * Replaces the launch in tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:255-256

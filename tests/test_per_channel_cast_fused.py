@@ -52,3 +52,19 @@ def test_per_channel_cast_fused_fixture(cuda_device, rnd, src, gather):
     out, sf = quant.per_channel_cast_fused(x, 'e4m3', 128, rnd, npc, pos)
     assert_equal(to_host(out), golden_tensor(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/out'))
     assert_equal(to_host(sf), golden_tensor(store, f'pc/{src}/r{int(rnd)}/g{int(gather)}/sf'))
+
+
+@pytest.mark.parametrize('round_sf', [False, True])
+@pytest.mark.parametrize('num_per_tokens', [32, 128])
+@pytest.mark.parametrize('num_tokens,hidden', [(4096, 576), (4096, 2048), (8064, 7168), (128, 64), (1024, 2560)])
+def test_per_channel_cast_and_transpose(oracle, cuda_device, num_tokens, hidden, num_per_tokens, round_sf):
+    """As the reference's tests/quant/test_per_channel_cast_and_transpose.py:41-52: the (n x 1)-block cast, data transposed."""
+    from tilekernels_b200 import quant
+    g = torch.Generator().manual_seed(num_tokens + hidden + num_per_tokens)
+    x = torch.randn((num_tokens, hidden), generator=g).to(torch.bfloat16)
+    x[3] *= 30
+    x[:, 5] = 0
+    out, sf = quant.per_channel_cast_and_transpose(x.to(cuda_device), 'e4m3', num_per_tokens, round_sf)
+    out_ref, sf_ref = oracle.cast(x, 'e4m3', (num_per_tokens, 1), round_sf=round_sf)
+    assert_equal(to_host(out), out_ref.view(torch.uint8).T.contiguous().view(torch.float8_e4m3fn))
+    assert_equal(to_host(sf), sf_ref)

@@ -93,13 +93,14 @@ __device__ __forceinline__ void issue_tile(const TileParams& p, const CUtensorMa
     tma_load_tile(stage, tmap, static_cast<int32_t>(c.col0), static_cast<int32_t>(c.row0), bar);
 }
 
-// The tile pipeline shared by both kernels.  Blocks are persistent: block b handles tiles b, b + grid, ...;
-// thread 0 keeps `stages` tile loads in flight; a stage is refilled as soon as every thread has copied its
-// part of the tile into registers.  `consume(i, coord, v)` does the arithmetic of one tile; it contains
-// block-wide barriers, so every thread calls it.
-template <int DT, class Consume>
-__device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUtensorMap* tmap, uint8_t* smem, uint64_t* full_bar,
-                                                  Consume consume) {
+// The tile pipeline shared by the tile kernels.  Blocks are persistent: block b handles tiles b, b + grid, ...;
+// thread 0 keeps `stages` tile loads in flight.  Per tile every thread calls `read(tile, coord)`, which copies
+// the thread's part of the tile from shared memory into registers; after the barrier that follows, the stage
+// is refilled and `consume(i, coord)` does the arithmetic (it contains block-wide barriers, so every thread
+// calls it).
+template <int DT, class Read, class Consume>
+__device__ __forceinline__ void run_tile_pipeline_rw(const TileParams& p, const CUtensorMap* tmap, uint8_t* smem, uint64_t* full_bar,
+                                                     Read read, Consume consume) {
     const uint32_t t = threadIdx.x;
     const uint32_t stages = p.stages;
     if (t == 0) {
@@ -112,7 +113,6 @@ __device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUt
         for (uint32_t i = 0; i < stages && i < my_tiles; ++i)
             issue_tile<DT>(p, tmap, first + i * step, smem + static_cast<size_t>(i) * TileElem<DT>::kTileBytes, full_bar + i);
     }
-    const int c16 = t & 7, r_base = t >> 3;
     for (uint32_t i = 0; i < my_tiles; ++i) {
         const uint32_t s = i % stages, parity = (i / stages) & 1;
         const TileCoord c = tile_coord(p, first + i * step);
@@ -120,27 +120,41 @@ __device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUt
             atomicExch(&g_tile_wait_failed, 1u);
             return;
         }
-        const uint8_t* tile = smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes;
-        float v[4][16];
-        const bool col_ok = c16 * 16 < c.valid_cols;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int r = r_base + 32 * k;
-            if (col_ok && r < c.valid_rows) {
-                read_chunk<DT>(tile, r, c16, v[k]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[k][j] = 0.0f;
-            }
-        }
+        read(smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes, c);
         // the reads above went through the generic proxy, the refill below goes through the async proxy:
         // order them before the barrier that lets thread 0 overwrite the stage
         fence_proxy_async_smem();
         __syncthreads();  // the stage is free again
         if (t == 0 && i + stages < my_tiles)
             issue_tile<DT>(p, tmap, first + (i + stages) * step, smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes, full_bar + s);
-        consume(i, c, v, col_ok);
+        consume(i, c);
     }
+}
+
+// The row-major register mapping used by the per-block and per-channel casts: thread t holds the 16-column chunk
+// t % 8 of rows t / 8 + 32 k, k = 0..3 (zeros outside the tensor); `consume(i, coord, v, col_ok)`.
+template <int DT, class Consume>
+__device__ __forceinline__ void run_tile_pipeline(const TileParams& p, const CUtensorMap* tmap, uint8_t* smem, uint64_t* full_bar,
+                                                  Consume consume) {
+    const int c16 = threadIdx.x & 7, r_base = threadIdx.x >> 3;
+    float v[4][16];
+    bool col_ok = false;
+    run_tile_pipeline_rw<DT>(
+        p, tmap, smem, full_bar,
+        [&](const uint8_t* tile, const TileCoord& c) {
+            col_ok = c16 * 16 < c.valid_cols;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = r_base + 32 * k;
+                if (col_ok && r < c.valid_rows) {
+                    read_chunk<DT>(tile, r, c16, v[k]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[k][j] = 0.0f;
+                }
+            }
+        },
+        [&](uint32_t i, const TileCoord& c) { consume(i, c, v, col_ok); });
 }
 
 // ---------------------------------------------------------------------------
@@ -282,6 +296,77 @@ __global__ void __launch_bounds__(kTileThreads) per_channel_cast_kernel(const __
             }
         }
     });
+}
+
+// ---------------------------------------------------------------------------
+// Per-channel cast with transposed output: one scale per (NPT tokens x 1 channel), NPT = 32 or 128, data written
+// as [hidden, num_tokens] (reference: tile_kernels/quant/per_channel_cast_and_transpose_kernel.py:85-123).
+// The tile is read from shared memory in the transposed sense: thread t owns channel t % 128 and the 64 tokens
+// (t / 128) * 64 ... of the tile, so a warp reads 64 contiguous bytes per token row (no bank conflicts), the
+// column maximum is mostly thread-local, and 16 consecutive tokens of a channel leave as one 128-bit store.
+// ---------------------------------------------------------------------------
+template <int NPT>
+__global__ void __launch_bounds__(kTileThreads) per_channel_cast_transpose_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                                                  const TileParams p) {
+    constexpr int kBlocksPerThread = 64 / (NPT < 64 ? NPT : 64);  // scale blocks inside a thread's 64 tokens: 2 or 1
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full_bar[8];
+    __shared__ float half_max[2][2][kTile];  // [tile parity][token half][channel], NPT = 128 only
+    const int t = threadIdx.x;
+    const int ch = t & 127, half = t >> 7;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    uint32_t packed[32];  // 64 bf16: tokens 2i (low half) and 2i + 1 (high half) of the thread's range
+
+    run_tile_pipeline_rw<TKQ_DT_BF16>(
+        p, &tmap, smem, full_bar,
+        [&](const uint8_t* tile, const TileCoord&) {
+            const uint16_t* src = reinterpret_cast<const uint16_t*>(tile) + static_cast<size_t>(half) * 64 * kTile + ch;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                packed[i] = static_cast<uint32_t>(src[(2 * i) * kTile]) | (static_cast<uint32_t>(src[(2 * i + 1) * kTile]) << 16);
+        },
+        [&](uint32_t i, const TileCoord& c) {
+            float m[kBlocksPerThread];
+#pragma unroll
+            for (int b = 0; b < kBlocksPerThread; ++b) {
+                m[b] = 0.0f;
+#pragma unroll
+                for (int q = 0; q < 32 / kBlocksPerThread; ++q) {
+                    const uint32_t w = packed[b * (32 / kBlocksPerThread) + q];
+                    m[b] = max3_abs(m[b], bf16_lo(w), bf16_hi(w));
+                }
+            }
+            if constexpr (NPT == 128) {
+                half_max[i & 1][half][ch] = m[0];
+                __syncthreads();
+                m[0] = fmaxf(half_max[i & 1][0][ch], half_max[i & 1][1][ch]);
+            }
+            const bool ch_ok = ch < c.valid_cols;
+            float inv[kBlocksPerThread];
+#pragma unroll
+            for (int b = 0; b < kBlocksPerThread; ++b) {
+                const Scale s = make_scale_for<TKQ_FMT_E4M3>(m[b], p.clamp_min, round_sf, p.fast_pow2);
+                inv[b] = s.inv;
+                const int64_t sf_row = NPT == 128 ? c.tile_m : c.tile_m * (kTile / NPT) + half * kBlocksPerThread + b;
+                const bool tokens_ok = NPT == 128 ? true : (half * 64 + b * NPT) < c.valid_rows;
+                if (ch_ok && tokens_ok && (NPT != 128 || half == 0)) static_cast<float*>(p.sf)[sf_row * p.hidden + c.col0 + ch] = s.sf;
+            }
+            if (!ch_ok) return;
+            uint8_t* dst = p.out + (c.col0 + ch) * p.num_tokens + c.row0 + half * 64;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {  // 16 tokens = 8 packed words -> 16 bytes
+                if (half * 64 + g * 16 >= c.valid_rows) break;
+                const float k = inv[kBlocksPerThread == 1 ? 0 : g / 2];
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t w0 = packed[g * 8 + 2 * q], w1 = packed[g * 8 + 2 * q + 1];
+                    o[q] = cvt_e4m3x4(__fmul_rn(bf16_lo(w0), k), __fmul_rn(bf16_hi(w0), k), __fmul_rn(bf16_lo(w1), k),
+                                      __fmul_rn(bf16_hi(w1), k));
+                }
+                stg128(dst + g * 16, o[0], o[1], o[2], o[3]);
+            }
+        });
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
@@ -567,4 +652,32 @@ extern "C" int tkq_per_channel_cast_fused(const void* x, int in_kind, const floa
     else if (in_kind == TKQ_DT_FP32) per_channel_cast_fused_kernel<TKQ_DT_FP32><<<grid, kTileThreads, 0, s>>>(p);
     else per_channel_cast_fused_kernel<kInFp8><<<grid, kTileThreads, 0, s>>>(p);
     return check_launch("per_channel_cast_fused");
+}
+
+extern "C" int tkq_per_channel_cast_and_transpose(const void* x, int64_t num_tokens, int64_t hidden, int num_per_tokens,
+                                                  unsigned flags, void* out, void* sf, void* stream) {
+    if (num_tokens < 0 || hidden <= 0) return set_error(TKQ_E_BAD_ARG, "per_channel_cast_and_transpose: bad size");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || sf == nullptr || out == nullptr) return set_error(TKQ_E_BAD_ARG, "per_channel_cast_and_transpose: null pointer");
+    if (flags & ~TKQ_ROUND_SF) return set_error(TKQ_E_UNSUPPORTED, "per_channel_cast_and_transpose: only TKQ_ROUND_SF is defined");
+    if (num_tokens % 128 != 0 || hidden % 64 != 0 || (num_per_tokens != 32 && num_per_tokens != 128))
+        return set_error(TKQ_E_UNSUPPORTED,
+                         "per_channel_cast_and_transpose: num_tokens % 128 == 0, hidden % 64 == 0, num_per_tokens 32 or 128 required");
+    if (!aligned16(x) || !aligned16(out) || (reinterpret_cast<uintptr_t>(sf) & 3u))
+        return set_error(TKQ_E_ALIGNMENT, "per_channel_cast_and_transpose: x and out must be 16-byte aligned, sf 4-byte aligned");
+    TileParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = sf;
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.sf_stride = hidden;
+    p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
+    p.flags = flags;
+    p.clamp_min = 1e-4f;
+    p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const char* what = "per_channel_cast_and_transpose";
+    return num_per_tokens == 128 ? launch_tile(per_channel_cast_transpose_kernel<128>, p, 2, what, s)
+                                 : launch_tile(per_channel_cast_transpose_kernel<32>, p, 2, what, s);
 }
