@@ -3,7 +3,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, 'lib', 'libtkquant.so')
+LIB_PATH = os.environ.get('TKQ_LIB_PATH') or os.path.join(_HERE, 'lib', 'libtkquant.so')
 
 # enums of include/tkquant.h
 DT_BF16, DT_FP32 = 0, 1

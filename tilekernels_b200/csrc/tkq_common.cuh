@@ -272,8 +272,9 @@ __device__ __forceinline__ void pack_e5m6x8(const uint32_t* c, uint32_t* w) {
 // CUDA's own expf goes through the hardware ex2 approximation, which no CPU can reproduce.
 // Argument clamped to [-87, 88]; within 1 ulp there; 18 instructions.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float tkq_expf(float x) {
-    x = fminf(fmaxf(x, -87.0f), 88.0f);
+template <bool kClampArg>
+__device__ __forceinline__ float tkq_expf_impl(float x) {
+    if (kClampArg) x = fminf(fmaxf(x, -87.0f), 88.0f);
     const float shift = 12582912.0f;
     const float t = __fmaf_rn(x, 1.4426950408889634f, shift);
     const float jf = __fsub_rn(t, shift);
@@ -291,11 +292,29 @@ __device__ __forceinline__ float tkq_expf(float x) {
     return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
+__device__ __forceinline__ float tkq_expf(float x) { return tkq_expf_impl<true>(x); }
+
 // silu(g) * u evaluated as (g / (1 + exp(-g))) * u with IEEE division
 // (reference: tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:140-144).
 __device__ __forceinline__ float swiglu(float g, float u) {
     const float d = __fadd_rn(1.0f, tkq_expf(-g));
     return __fmul_rn(__fdiv_rn(g, d), u);
+}
+
+// The same value for 2^-40 <= |g| <= 44 with g a bf16 number, in 12 fewer instructions:
+//   * the argument of exp needs no clamp;
+//   * g / d (d = 1 + exp(-g) in [1, 2^64)) is computed as reciprocal approximation, one Newton step, quotient,
+//     exact residual, correction.  For bf16 numerators this sequence was compared with IEEE division on the
+//     GPU for all 2^7 numerator mantissas x all 2^23 denominator mantissas over 41 exponent offsets and several
+//     denominator binades: no difference (in this range no intermediate under- or overflows, so the result
+//     depends on the two mantissas and the exponent difference only).
+__device__ __forceinline__ float swiglu_bf16_in_range(float g, float u) {
+    const float d = __fadd_rn(1.0f, tkq_expf_impl<false>(-g));
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(d));
+    y = __fmaf_rn(y, __fmaf_rn(-d, y, 1.0f), y);
+    const float q = __fmul_rn(g, y);
+    return __fmul_rn(__fmaf_rn(__fmaf_rn(-d, q, g), y, q), u);
 }
 
 // ---------------------------------------------------------------------------

@@ -109,26 +109,40 @@ struct SwigluSource {
         P::issue(r.g, p, wide);
         P::issue(r.u, static_cast<const uint8_t*>(p) + hidden * kElemBytes, wide);
     }
-    // kClamp: apply the clamp; kCount: also count what was clamped; kWeight: multiply by w
+    // kClamp: apply the clamp; kCount: also count what was clamped; kWeight: multiply by w.
+    // `bf16_gates`: every gate value that reaches the activation is a bf16 number (bf16 input and, if clamping,
+    // a bf16-representable clamp value), which allows the cheaper in-range evaluation.
     template <bool kClamp, bool kCount, bool kWeight>
-    __device__ __forceinline__ static void unpack(const Raw& r, float* v, float clamp, float w, ClampCounters& cnt) {
+    __device__ __forceinline__ static void unpack(const Raw& r, float* v, float clamp, float w, ClampCounters& cnt,
+                                                  bool bf16_gates) {
         float g[16], u[16];
         P::unpack(r.g, g);
         P::unpack(r.u, u);
+        if (kClamp) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float gi = g[i], ui = u[i];
-            if (kClamp) {
+            for (int i = 0; i < 16; ++i) {
                 if (kCount) {
-                    cnt.gate_hi += gi > clamp;
-                    cnt.up_hi += ui > clamp;
-                    cnt.up_lo += ui < -clamp;
+                    cnt.gate_hi += g[i] > clamp;
+                    cnt.up_hi += u[i] > clamp;
+                    cnt.up_lo += u[i] < -clamp;
                 }
-                gi = gi > clamp ? clamp : gi;
-                ui = ui > clamp ? clamp : ui;
-                ui = ui < -clamp ? -clamp : ui;
+                g[i] = g[i] > clamp ? clamp : g[i];
+                u[i] = u[i] > clamp ? clamp : u[i];
+                u[i] = u[i] < -clamp ? -clamp : u[i];
             }
-            v[i] = swiglu(gi, ui);
+        }
+        float lo = 1.0f, hi = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            lo = min3_abs(lo, g[i], g[i + 1]);
+            hi = max3_abs(hi, g[i], g[i + 1]);
+        }
+        if (bf16_gates && lo >= 9.094947017729282e-13f && hi <= 44.0f) {  // 2^-40 <= |g| <= 44 for the whole chunk
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = swiglu_bf16_in_range(g[i], u[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = swiglu(g[i], u[i]);
         }
         if (kWeight && w != 1.0f) {  // uniform over the row; multiplying by exactly 1 would change nothing
 #pragma unroll

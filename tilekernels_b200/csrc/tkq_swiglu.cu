@@ -1,4 +1,6 @@
 // C entry point of the fused SwiGLU + per-token e4m3 cast.
+#include <cstring>
+
 #include "tkq_launch.cuh"
 #include "tkq_token_kernels.cuh"
 
@@ -85,6 +87,11 @@ extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype
     p.topk_weights = topk_weights;
     p.pos_to_expert = pos_to_expert;
     p.swiglu_clamp = swiglu_clamp;
+    {
+        uint32_t clamp_bits;
+        std::memcpy(&clamp_bits, &swiglu_clamp, 4);
+        p.bf16_gates = in_dtype == TKQ_DT_BF16 && (swiglu_clamp < 0.0f || (clamp_bits & 0xFFFFu) == 0);
+    }
     p.clamped_count = reinterpret_cast<unsigned long long*>(clamped_count);
     p.num_groups = per_row_scale ? 1u : static_cast<uint32_t>(hidden / 128);
     p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 448.0f);

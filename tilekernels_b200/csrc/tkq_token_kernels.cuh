@@ -41,6 +41,7 @@ struct TokenCastParams {
     const float* topk_weights;
     const int32_t* pos_to_expert;
     float swiglu_clamp;
+    bool bf16_gates;  // SwiGLU: bf16 input and (no clamp or a bf16-representable clamp value)
     unsigned long long* clamped_count;
     // already quantized input only: its scales (layouts as for the output scales) and their block shape
     const void* in_sf;
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
             const uint32_t col = col0 + u * 512u;
             if (U > 1 && col - lane * 16u >= hidden) break;  // warp-uniform: the whole step lies beyond the row
             float v[16];
-            if constexpr (kSwiglu) Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt);
+            if constexpr (kSwiglu) Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[u], v, p.swiglu_clamp, w, cnt, p.bf16_gates);
             else if constexpr (kQuant) Src::unpack(raw[u], v, col < hidden ? load_input_scale(p, this_row, col) : 0.0f);
             else Src::unpack(raw[u], v);
             const bool in_row = col < hidden;
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(kRowMaxThreads) row_cast_kernel(const TokenCas
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             if constexpr (kSwiglu)
-                Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[k], v[k], p.swiglu_clamp, w, cnt);
+                Src::template unpack<(kClampMode > 0), (kClampMode > 1), true>(raw[k], v[k], p.swiglu_clamp, w, cnt, p.bf16_gates);
             else
                 Src::unpack(raw[k], v[k]);
             amax = fmaxf(amax, absmax16(v[k]));
