@@ -177,19 +177,40 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
          lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)),
         ('cfg4 per_token_cast e5m6 [32768,7168]', 'cfg4', None, lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
     ]
+    ue = dict(use_tma_aligned_col_major_sf=True, round_sf=True, use_packed_ue8m0=True)
+    gather = torch.randint(0, 7168, (8192,), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
+    gather[::11] = -1
+    gather = gather.to(device)
+    # the rows next to the hot path (dequantisation, re-quantisation, fused / transposing per-channel casts):
+    # `prepare` turns the bf16 workload tensor into the op's input
+    specs += [
+        ('cfg4 per_token_cast_back e4m3 g128 ue8m0 -> bf16 [32768,7168]', 'cfg4', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, **ue),
+         lambda q: (quant.per_token_cast_back(q, 'bf16', 128),)),
+        ('cfg4 per_token_cast_back e5m6 -> bf16 [32768,7168]', 'cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1]),
+         lambda q: (quant.per_token_cast_back(q, 'bf16', 7168, x_special_fmt='e5m6'),)),
+        ('cfg4 per_token_cast e4m3 g128 of FP8 input with 128x128 ue8m0 scales [32768,7168]', 'cfg4',
+         lambda x: quant.per_block_cast(x, 'e4m3', (128, 128), **ue), lambda q: quant.per_token_cast(q, 'e4m3', 128, (128, 128), **ue)),
+        ('cfg2 per_channel_cast_fused bf16 + gather of 8192 rows [7168,2048]', 'cfg2', None,
+         lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gather)),
+        ('cfg2 per_channel_cast_and_transpose 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128)),
+    ]
+
+    def clone(v):
+        return tuple(clone(t) for t in v) if isinstance(v, tuple) else v.clone()
+
     cache, results = {}, []
-    for label, cfg, _, op in specs:
+    for label, cfg, prepare, op in specs:
         if cfg not in cache:
             cache.clear()
             cache[cfg] = make_config_input(cfg).to(device)
-        x = cache[cfg]
+        x = cache[cfg] if prepare is None else prepare(cache[cfg])
         out = op(x)
         nbytes = count_bytes(x, out)
         sets = max(2, -(-2 * L2_BYTES // nbytes) + 1)
         del out
-        xs = [x] + [x.clone() for _ in range(sets - 1)]
+        xs = [x] + [clone(x) for _ in range(sets - 1)]
         med, best = time_graph(torch, op, xs, launches=2 * sets)
-        del xs
+        del xs, x
         torch.cuda.empty_cache()
         results.append({'op': label, 'bytes': nbytes, 'us_median': round(med, 2), 'us_min': round(best, 2),
                         'gbs': round(nbytes / med / 1e3, 1), 'frac_of_hbm_peak': round(nbytes / med / 1e3 / peak, 3),

@@ -163,6 +163,20 @@ int tkq_per_channel_cast_fused(const void* x, int in_kind, const float* x_sf, co
                                void* sf, void* stream);
 
 /*
+ * Fused SwiGLU + per-channel e4m3 cast, optionally transposed: y = silu(x[:, :hidden]) * x[:, hidden:] in fp32
+ * (optionally clamped as in tkq_swiglu_forward_and_per_token_cast), ROUNDED TO BF16, then one scale per
+ * (num_per_tokens tokens x 1 channel), num_per_tokens = 32 or 128.
+ * Replaces the launch in tile_kernels/quant/swiglu_forward_and_per_channel_cast_and_transpose_kernel.py:226-227.
+ *
+ *   x          [num_tokens, 2 * hidden] bf16, contiguous, num_tokens % 128 == 0, hidden % 64 == 0
+ *   transpose  non-zero: out is [hidden, num_tokens]; zero: [num_tokens, hidden]
+ *   sf         [num_tokens / num_per_tokens, hidden] fp32
+ * flags: TKQ_ROUND_SF only.
+ */
+int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t num_tokens, int64_t hidden, int num_per_tokens, int transpose,
+                                            float swiglu_clamp, unsigned flags, void* out, void* sf, void* stream);
+
+/*
  * Dequantise: out = float(x) * scale of the value's block, formed in fp32 and rounded once to bf16 or fp32.
  * Replaces the launches in tile_kernels/quant/cast_back_kernel.py:118-119 (cast_back, per_token_cast_back;
  * kernel :51-72) and tile_kernels/quant/cast_back_e5m6_kernel.py (cast_back_e5m6).

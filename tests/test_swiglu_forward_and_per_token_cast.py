@@ -89,3 +89,26 @@ def test_custom_sf_clamp_min(oracle, cuda_device):
     out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x_cpu), 'e4m3', (1, 128), clamp_min=1e-2)
     assert_equal(to_host(out), out_ref)
     assert_equal(to_host(sf), sf_ref)
+
+
+@pytest.mark.parametrize('clamp', [None, 10.0, 0.5, 0.3])
+@pytest.mark.parametrize('round_sf', [False, True])
+@pytest.mark.parametrize('without_transpose', [False, True])
+@pytest.mark.parametrize('num_per_tokens', [32, 128])
+@pytest.mark.parametrize('num_tokens,hidden', [(4096, 1024), (1024, 3584), (128, 64), (384, 1280)])
+def test_swiglu_forward_and_per_channel_cast_and_transpose(oracle, cuda_device, num_tokens, hidden, num_per_tokens, without_transpose,
+                                                           round_sf, clamp):
+    """As the reference's tests/quant/test_swiglu_forward_and_per_channel_cast_and_transpose.py:44-85: the bf16-rounded
+    activation is cast per (n x 1) block; data transposed unless without_transpose."""
+    from tilekernels_b200 import quant
+    gen = torch.Generator().manual_seed(num_tokens + hidden + num_per_tokens)
+    x = (torch.randn((num_tokens, 2 * hidden), generator=gen) * 1.5).to(torch.bfloat16)
+    x[7] = 0
+    out, sf = quant.swiglu_forward_and_per_channel_cast_and_transpose(x.to(cuda_device), 'e4m3', num_per_tokens, round_sf,
+                                                                        without_transpose, clamp)
+    act = oracle.swiglu_forward(x, swiglu_clamp_value=clamp).bfloat16()
+    out_ref, sf_ref = oracle.cast(act, 'e4m3', (num_per_tokens, 1), round_sf=round_sf)
+    if not without_transpose:
+        out_ref = out_ref.view(torch.uint8).T.contiguous().view(torch.float8_e4m3fn)
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)

@@ -67,12 +67,20 @@ __global__ void __launch_bounds__(kGroupThreads) cast_back_kernel(const TokenCas
         const float scale = load_input_scale(p, this_row, col);
         float v[16];
         Src::unpack(raw, v, scale);
+        // a lane's output is 32 (bf16) or 64 (fp32) contiguous bytes at a 32-byte aligned address (out is 32-byte
+        // aligned when wide_stores is set, hidden is a multiple of 16): one or two 256-bit stores
         if constexpr (OUT_DT == TKQ_DT_FP32) {
             float* dst = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(this_row) * p.hidden + col;
+            uint32_t w[16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                stg128(dst + 4 * q, __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]), __float_as_uint(v[4 * q + 2]),
-                       __float_as_uint(v[4 * q + 3]));
+            for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
+            if (p.wide_loads) {
+                stg256(dst, w);
+                stg256(dst + 8, w + 8);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) stg128(dst + 4 * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            }
         } else {
             uint32_t w[8];
 #pragma unroll
@@ -81,8 +89,12 @@ __global__ void __launch_bounds__(kGroupThreads) cast_back_kernel(const TokenCas
                 w[i] = *reinterpret_cast<const uint32_t*>(&b);
             }
             uint8_t* dst = p.out + (static_cast<int64_t>(this_row) * p.hidden + col) * 2;
-            stg128(dst, w[0], w[1], w[2], w[3]);
-            stg128(dst + 16, w[4], w[5], w[6], w[7]);
+            if (p.wide_loads) {
+                stg256(dst, w);
+            } else {
+                stg128(dst, w[0], w[1], w[2], w[3]);
+                stg128(dst + 16, w[4], w[5], w[6], w[7]);
+            }
         }
     }
 }
@@ -126,6 +138,7 @@ extern "C" int tkq_cast_back(const void* x, int in_fmt, const void* x_sf, unsign
     p.in_sf_flags = x_sf_flags;
     p.in_block_m = static_cast<uint32_t>(x_block_m);
     p.in_block_k = static_cast<uint32_t>(x_block_k);
+    p.wide_loads = reinterpret_cast<uintptr_t>(out) % 32 == 0;  // here: 256-bit *stores* are legal
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (in_fmt == TKQ_FMT_E4M3) return launch_cast_back<QuantSource<TKQ_FMT_E4M3>>(p, out_dtype, s);
     if (in_fmt == TKQ_FMT_E2M1) return launch_cast_back<QuantSource<TKQ_FMT_E2M1>>(p, out_dtype, s);

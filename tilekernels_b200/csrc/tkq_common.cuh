@@ -48,6 +48,13 @@ __device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t
                  : "memory");
 }
 
+// 256-bit store; p must be 32-byte aligned
+__device__ __forceinline__ void stg256(void* p, const uint32_t* w) {
+    asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ void stg64(void* p, uint32_t a, uint32_t b) {
     asm volatile("st.global.L1::no_allocate.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }

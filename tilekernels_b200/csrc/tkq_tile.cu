@@ -9,6 +9,9 @@
 // store instruction.
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+
+#include <cstring>
 
 #include "tkq_async.cuh"
 #include "tkq_launch.cuh"
@@ -369,6 +372,122 @@ __global__ void __launch_bounds__(kTileThreads) per_channel_cast_transpose_kerne
         });
 }
 
+// ---------------------------------------------------------------------------
+// Fused SwiGLU + per-channel cast (+ transpose): the activation silu(gate) * up is formed in fp32, rounded to
+// bf16, and that bf16 tile is cast with one scale per (NPT tokens x 1 channel), written either as
+// [num_tokens, hidden] or transposed (reference:
+// tile_kernels/quant/swiglu_forward_and_per_channel_cast_and_transpose_kernel.py:177-231; its test quantises
+// the bf16-rounded activation, tests/quant/test_swiglu_forward_and_per_channel_cast_and_transpose.py:63-66).
+// One block per 128 x 128 output tile: the activation tile is built in shared memory from plain vector loads
+// of the two input halves, then read back in whichever register mapping suits the output layout.
+// ---------------------------------------------------------------------------
+struct SwigluChannelParams {
+    const void* x;  // [num_tokens, 2 * hidden] bf16
+    uint8_t* out;
+    float* sf;
+    int64_t num_tokens, hidden;
+    uint32_t tiles_k;
+    uint32_t flags;
+    float clamp_min;
+    float swiglu_clamp;  // < 0: none
+    bool fast_pow2;
+    bool bf16_gates;
+    bool wide_loads;
+};
+
+template <int NPT, bool kTranspose>
+__global__ void __launch_bounds__(kTileThreads) swiglu_per_channel_cast_kernel(const SwigluChannelParams p) {
+    constexpr int NRB = kTile / NPT;  // scale blocks along the tokens of a tile: 1 or 4
+    __shared__ __align__(16) uint16_t act[kTile][kTile];  // the bf16 activation tile
+    __shared__ int col_amax_bits[NRB][kTile];
+    __shared__ float col_inv[NRB][kTile];
+    using Src = SwigluSource<TKQ_DT_BF16>;
+    const int t = threadIdx.x, lane = t & 31;
+    const int c16 = t & 7, r_base = t >> 3;
+    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
+    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
+    const int valid_cols = static_cast<int>(p.hidden - col0 < kTile ? p.hidden - col0 : kTile);
+    const bool col_ok = c16 * 16 < valid_cols;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    for (int i = t; i < NRB * kTile; i += kTileThreads) (&col_amax_bits[0][0])[i] = 0;
+
+    // 1. activation tile -> shared memory (num_tokens is a multiple of 128: every tile row exists)
+    ClampCounters unused;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = r_base + 32 * k;
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (col_ok) {
+            typename Src::Raw raw;
+            Src::issue(raw, static_cast<const uint8_t*>(p.x) + ((row0 + r) * 2 * p.hidden + col0 + c16 * 16) * 2, p.wide_loads, p.hidden);
+            float y[16];
+            if (p.swiglu_clamp >= 0.0f) Src::template unpack<true, false, false>(raw, y, p.swiglu_clamp, 1.0f, unused, p.bf16_gates);
+            else Src::template unpack<false, false, false>(raw, y, 0.0f, 1.0f, unused, p.bf16_gates);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(&act[r][c16 * 16]);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    __syncthreads();
+
+    // 2. column maxima per scale block: thread t < 128 * NRB scans its channel over NPT tokens (conflict-free:
+    //    consecutive threads read consecutive channels)
+    for (int i = t; i < NRB * kTile; i += kTileThreads) {
+        const int rb = i / kTile, ch = i % kTile;
+        float m = 0.0f;
+#pragma unroll 8
+        for (int r = 0; r < NPT; r += 2)
+            m = max3_abs(m, __uint_as_float(static_cast<uint32_t>(act[rb * NPT + r][ch]) << 16),
+                         __uint_as_float(static_cast<uint32_t>(act[rb * NPT + r + 1][ch]) << 16));
+        const Scale s = make_scale_for<TKQ_FMT_E4M3>(m, p.clamp_min, round_sf, p.fast_pow2);
+        col_inv[rb][ch] = s.inv;
+        if (ch < valid_cols) p.sf[(tile_m * NRB + rb) * p.hidden + col0 + ch] = s.sf;
+    }
+    __syncthreads();
+
+    // 3. convert and store
+    if constexpr (!kTranspose) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (!col_ok) continue;
+            float v[16], q[16];
+            read_chunk<TKQ_DT_BF16>(reinterpret_cast<const uint8_t*>(&act[0][0]), r, c16, v);
+            const float* inv = col_inv[r / NPT] + c16 * 16;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) q[j] = __fmul_rn(v[j], inv[j]);
+            stg128(p.out + (row0 + r) * p.hidden + col0 + c16 * 16, cvt_e4m3x4(q[0], q[1], q[2], q[3]), cvt_e4m3x4(q[4], q[5], q[6], q[7]),
+                   cvt_e4m3x4(q[8], q[9], q[10], q[11]), cvt_e4m3x4(q[12], q[13], q[14], q[15]));
+        }
+    } else {
+        // thread = (channel, 64 tokens): 16 consecutive tokens of a channel leave as one 128-bit store
+        const int ch = t & 127, half = t >> 7;
+        if (ch < valid_cols) {
+            uint8_t* dst = p.out + (col0 + ch) * p.num_tokens + row0 + half * 64;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int r0 = half * 64 + g * 16;
+                const float k = col_inv[r0 / NPT][ch];
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float f[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) f[e] = __fmul_rn(__uint_as_float(static_cast<uint32_t>(act[r0 + 4 * q + e][ch]) << 16), k);
+                    o[q] = cvt_e4m3x4(f[0], f[1], f[2], f[3]);
+                }
+                stg128(dst + g * 16, o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+    (void)lane;
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
 static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
@@ -680,4 +799,44 @@ extern "C" int tkq_per_channel_cast_and_transpose(const void* x, int64_t num_tok
     const char* what = "per_channel_cast_and_transpose";
     return num_per_tokens == 128 ? launch_tile(per_channel_cast_transpose_kernel<128>, p, 2, what, s)
                                  : launch_tile(per_channel_cast_transpose_kernel<32>, p, 2, what, s);
+}
+
+extern "C" int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t num_tokens, int64_t hidden, int num_per_tokens,
+                                                       int transpose, float swiglu_clamp, unsigned flags, void* out, void* sf,
+                                                       void* stream) {
+    if (num_tokens < 0 || hidden <= 0) return set_error(TKQ_E_BAD_ARG, "swiglu per-channel cast: bad size");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || sf == nullptr || out == nullptr) return set_error(TKQ_E_BAD_ARG, "swiglu per-channel cast: null pointer");
+    if (flags & ~TKQ_ROUND_SF) return set_error(TKQ_E_UNSUPPORTED, "swiglu per-channel cast: only TKQ_ROUND_SF is defined");
+    if (num_tokens % 128 != 0 || hidden % 64 != 0 || (num_per_tokens != 32 && num_per_tokens != 128))
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu per-channel cast: num_tokens % 128 == 0, hidden % 64 == 0, num_per_tokens 32 or 128 required");
+    if (!aligned16(x) || !aligned16(out) || (reinterpret_cast<uintptr_t>(sf) & 3u))
+        return set_error(TKQ_E_ALIGNMENT, "swiglu per-channel cast: x and out must be 16-byte aligned, sf 4-byte aligned");
+    SwigluChannelParams p{};
+    p.x = x;
+    p.out = static_cast<uint8_t*>(out);
+    p.sf = static_cast<float*>(sf);
+    p.num_tokens = num_tokens;
+    p.hidden = hidden;
+    p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
+    p.flags = flags;
+    p.clamp_min = 1e-4f;
+    p.swiglu_clamp = swiglu_clamp;
+    p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
+    uint32_t clamp_bits;
+    std::memcpy(&clamp_bits, &swiglu_clamp, 4);
+    p.bf16_gates = swiglu_clamp < 0.0f || (clamp_bits & 0xFFFFu) == 0;
+    p.wide_loads = reinterpret_cast<uintptr_t>(x) % 32 == 0 && (hidden * 2) % 32 == 0;
+    const int64_t tiles = (num_tokens / kTile) * p.tiles_k;
+    if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>(tiles);
+    if (num_per_tokens == 128) {
+        if (transpose) swiglu_per_channel_cast_kernel<128, true><<<grid, kTileThreads, 0, s>>>(p);
+        else swiglu_per_channel_cast_kernel<128, false><<<grid, kTileThreads, 0, s>>>(p);
+    } else {
+        if (transpose) swiglu_per_channel_cast_kernel<32, true><<<grid, kTileThreads, 0, s>>>(p);
+        else swiglu_per_channel_cast_kernel<32, false><<<grid, kTileThreads, 0, s>>>(p);
+    }
+    return check_launch("swiglu_forward_and_per_channel_cast_and_transpose");
 }
