@@ -177,6 +177,22 @@ int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t num_tokens, i
                                             float swiglu_clamp, unsigned flags, void* out, void* sf, void* stream);
 
 /*
+ * Lossless FP4 -> FP8 re-blocking: packed e2m1 input with power-of-two scales per (x_block_m x x_block_k) block
+ * becomes e4m3 with power-of-two scales per (out_block_m x out_block_k) block.  Output exponent of a block =
+ * (largest input exponent inside it) - 6, not below 0; value = fp4 * 2^(e_in - e_out).
+ * Replaces the launch in tile_kernels/quant/per_block_cast_lossless_kernel.py:201-202 (kernel :76-150).  The
+ * reference asserts e_in + 5 >= e_out on the device (exact representability); this library rounds to nearest
+ * where that does not hold.
+ *
+ *   x          [num_tokens, hidden / 2] bytes, x_row_stride in VALUES; x_sf as in tkq_per_token_cast_quantized
+ *   out blocks (1 | 32 | 128) x (32 | 128), multiples of the input block; hidden % 32 == 0
+ *   flags      TKQ_SF_COL_MAJOR, TKQ_SF_UE8M0 for the output scales (always powers of two)
+ */
+int tkq_per_block_cast_lossless(const void* x, const void* x_sf, unsigned x_sf_flags, int64_t x_sf_stride, int x_block_m,
+                                int x_block_k, int64_t num_tokens, int64_t hidden, int64_t x_row_stride, int out_block_m,
+                                int out_block_k, unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream);
+
+/*
  * Dequantise: out = float(x) * scale of the value's block, formed in fp32 and rounded once to bf16 or fp32.
  * Replaces the launches in tile_kernels/quant/cast_back_kernel.py:118-119 (cast_back, per_token_cast_back;
  * kernel :51-72) and tile_kernels/quant/cast_back_e5m6_kernel.py (cast_back_e5m6).

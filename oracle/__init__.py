@@ -149,6 +149,30 @@ def cast_back_from_e5m6(x, fmt: str, x_block_size) -> torch.Tensor:
     return out if fmt == 'fp32' else out.bfloat16()
 
 
+def per_block_cast_lossless(x, x_block_size, out_block_size, use_tma_aligned_col_major_sf: bool = False,
+                            use_packed_ue8m0: bool = False):
+    """Restatement of the reference kernel tile_kernels/quant/per_block_cast_lossless_kernel.py:96-131 (it has no
+    PyTorch counterpart; its test checks that both sides dequantise to the same fp32 values): output exponent =
+    max input exponent in the block - 6, not below 0; value = fp4 * 2^(e_in - e_out) cast to e4m3."""
+    q, sf = x
+    T = q.shape[0]
+    H = q.shape[1] * 2
+    ibm, ibk = x_block_size
+    obm, obk = out_block_size
+    e_in = (sf_to_float(sf)[:, :_ceil_div(H, ibk)].contiguous().view(torch.int32) >> 23)  # [T/ibm, H/ibk]
+    e_elem = e_in.repeat_interleave(ibm, 0)[:T].repeat_interleave(ibk, 1)[:, :H]
+    nm, nk = _ceil_div(T, obm), _ceil_div(H, obk)
+    padded = torch.zeros((nm * obm, nk * obk), dtype=torch.int32)
+    padded[:T, :H] = e_elem
+    e_out = padded.view(nm, obm, nk, obk).amax(dim=(1, 3))
+    e_out = torch.where(e_out >= 6, e_out - 6, torch.zeros_like(e_out))
+    e_out_elem = e_out.repeat_interleave(obm, 0)[:T].repeat_interleave(obk, 1)[:, :H]
+    rel = ((e_elem - e_out_elem + 127) << 23).view(torch.float32)
+    fp4 = cast_back((q, torch.ones((T, H // 32), dtype=torch.float32)), 'fp32', (1, 32))  # the bare e2m1 values
+    out = (fp4 * rel).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return out, format_sf((e_out << 23).contiguous(), use_tma_aligned_col_major_sf, use_packed_ue8m0)
+
+
 def sf_to_float(sf: torch.Tensor) -> torch.Tensor:
     """fp32 scales unchanged; packed int32 ue8m0 words -> fp32 [nm, 4*words] (cast.py:28-37)."""
     if sf.dtype == torch.float32:

@@ -70,3 +70,36 @@ def test_per_channel_cast_rejects_ragged_tokens(cuda_device):
     from tilekernels_b200 import quant
     with pytest.raises(AssertionError):
         quant.per_channel_cast(torch.zeros((100, 128), dtype=torch.bfloat16, device=cuda_device), 'e4m3', 128)
+
+
+def _clamp_abs_ratio(x, max_ratio=2.0 ** 10):
+    """Limit the dynamic range inside every 128 x 128 block so that the re-blocking is lossless."""
+    a = x.abs().clamp_min(1e-30)
+    T, H = x.shape
+    pad = torch.nn.functional.pad(a, (0, (-H) % 128, 0, (-T) % 128), value=0)
+    bmax = pad.view(pad.shape[0] // 128, 128, pad.shape[1] // 128, 128).amax(dim=(1, 3))
+    floor = (bmax / max_ratio).repeat_interleave(128, 0)[:T].repeat_interleave(128, 1)[:, :H]
+    return torch.where(a < floor, torch.sign(x) * floor + (x == 0) * floor, x)
+
+
+@pytest.mark.parametrize('out_flags', [(False, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('in_flags', [(False, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('out_block', [(1, 128), (32, 32), (128, 128)], ids=lambda b: f'{b[0]}x{b[1]}')
+@pytest.mark.parametrize('num_tokens,hidden', [(4001, 576), (4001, 7168), (129, 2048)])
+def test_per_block_cast_lossless(oracle, cuda_device, num_tokens, hidden, out_block, in_flags, out_flags):
+    """As the reference's tests/quant/test_per_block_cast_lossless.py:82-97: FP4 with (1, 32) power-of-two scales is
+    re-blocked to FP8; both sides must dequantise to identical fp32 values.  Also bit-exact against the oracle."""
+    from tilekernels_b200 import quant
+    g = torch.Generator().manual_seed(num_tokens + hidden)
+    x = _clamp_abs_ratio(torch.randn((num_tokens, hidden), generator=g) * 2.0 ** torch.randint(-20, 20, (1,), generator=g).item())
+    icol, irnd, iue = in_flags
+    ocol, ornd, oue = out_flags
+    q_ref, qsf_ref = oracle.cast(x, 'e2m1', (1, 32), round_sf=irnd, use_tma_aligned_col_major_sf=icol, use_packed_ue8m0=iue)
+    q, qsf = quant.per_token_cast(x.to(cuda_device), 'e2m1', 32, None, icol, irnd, iue)
+    out, sf = quant.per_block_cast_lossless((q, qsf), 'e4m3', (1, 32), out_block, ocol, ornd, oue)
+    out_ref, sf_ref = oracle.per_block_cast_lossless((q_ref, qsf_ref), (1, 32), out_block, ocol, oue)
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)
+    back_in = oracle.cast_back((q_ref, qsf_ref), 'fp32', (1, 32))
+    back_out = oracle.cast_back((to_host(out), to_host(sf)), 'fp32', out_block)
+    assert_equal(back_out, back_in)

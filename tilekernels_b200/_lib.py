@@ -25,6 +25,7 @@ SIGNATURES = {
     'tkq_per_channel_cast_fused': [_vp, _int, _vp, _vp, _i64, _i64, _i64, _uint, _vp, _vp, _vp],
     'tkq_per_channel_cast_and_transpose': [_vp, _i64, _i64, _int, _uint, _vp, _vp, _vp],
     'tkq_swiglu_forward_and_per_channel_cast': [_vp, _i64, _i64, _int, _int, _f32, _uint, _vp, _vp, _vp],
+    'tkq_per_block_cast_lossless': [_vp, _vp, _uint, _i64, _int, _int, _i64, _i64, _i64, _int, _int, _uint, _vp, _vp, _i64, _vp],
     'tkq_cast_back': [_vp, _int, _vp, _uint, _i64, _int, _int, _i64, _i64, _int, _vp, _vp],
     'tkq_swiglu_forward_and_per_token_cast': [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _f32, _vp, _f32, _int, _uint,
                                               _vp, _vp, _i64, _vp],

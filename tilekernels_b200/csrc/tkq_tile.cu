@@ -15,7 +15,7 @@
 
 #include "tkq_async.cuh"
 #include "tkq_launch.cuh"
-#include "tkq_sources.cuh"
+#include "tkq_token_kernels.cuh"
 
 namespace tkq {
 
@@ -488,6 +488,78 @@ __global__ void __launch_bounds__(kTileThreads) swiglu_per_channel_cast_kernel(c
     (void)lane;
 }
 
+// ---------------------------------------------------------------------------
+// Lossless FP4 -> FP8 re-blocking: the input is packed e2m1 with power-of-two scales per (in_bm x in_bk) block;
+// the output is e4m3 with power-of-two scales per (out_bm x out_bk) block.  The output exponent of a block is the
+// largest input exponent inside it minus 6 (not below 0); every value becomes fp4 * 2^(e_in - e_out), which e4m3
+// represents exactly as long as e_in + 5 >= e_out (reference: tile_kernels/quant/per_block_cast_lossless_kernel.py:
+// 96-131; where the reference asserts that condition on the device, this kernel rounds to nearest instead).
+// One block per 128 x 128 tile, plain vector loads, exponent maxima through shared-memory atomics.
+// ---------------------------------------------------------------------------
+struct LosslessParams {
+    TokenCastParams in;  // x, in_sf*, in_block_*, num_tokens, hidden (load_input_scale reads these)
+    void* sf;
+    int64_t sf_stride;
+    uint32_t out_bm, out_bk;
+    uint32_t tiles_k;
+    uint32_t flags;
+};
+
+__global__ void __launch_bounds__(kTileThreads) per_block_cast_lossless_kernel(const LosslessParams p) {
+    __shared__ int exp_max[kTile * 4];  // up to 128 x 4 output blocks per tile (out block 1 x 32)
+    const int t = threadIdx.x;
+    const int c16 = t & 7, r_base = t >> 3;
+    const int64_t hidden = p.in.hidden;
+    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
+    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
+    const int valid_rows = static_cast<int>(p.in.num_tokens - row0 < kTile ? p.in.num_tokens - row0 : kTile);
+    const int valid_cols = static_cast<int>(hidden - col0 < kTile ? hidden - col0 : kTile);
+    const int nrb = kTile / p.out_bm, ncb = kTile / p.out_bk;
+    for (int i = t; i < nrb * ncb; i += kTileThreads) exp_max[i] = 0;
+    __syncthreads();
+
+    const bool col_ok = c16 * 16 < valid_cols;
+    const int cb = c16 * 16 / p.out_bk;
+    uint32_t e_in[4];
+    QuantSource<TKQ_FMT_E2M1>::Raw raw[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = r_base + 32 * k;
+        e_in[k] = 0;
+        QuantSource<TKQ_FMT_E2M1>::zero(raw[k]);
+        if (col_ok && r < valid_rows) {
+            const int64_t elem = (row0 + r) * p.in.x_stride + col0 + c16 * 16;
+            QuantSource<TKQ_FMT_E2M1>::issue(raw[k], static_cast<const uint8_t*>(p.in.x) + elem / 2, false);
+            e_in[k] = __float_as_uint(load_input_scale(p.in, static_cast<uint32_t>(row0 + r), static_cast<uint32_t>(col0 + c16 * 16))) >> 23;
+            atomicMax(&exp_max[(r / p.out_bm) * ncb + cb], static_cast<int>(e_in[k]));
+        }
+    }
+    __syncthreads();
+    const int64_t num_kb = (hidden + p.out_bk - 1) / p.out_bk;
+    for (int i = t; i < nrb * ncb; i += kTileThreads) {
+        const int rb = i / ncb, kb = i % ncb;
+        if (rb * static_cast<int>(p.out_bm) < valid_rows && kb * static_cast<int>(p.out_bk) < valid_cols) {
+            const uint32_t e = exp_max[i] >= 6 ? exp_max[i] - 6 : 0;
+            const int64_t m_idx = tile_m * nrb + rb, k_idx = tile_k * ncb + kb;
+            if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_byte(p.sf, p.sf_stride, m_idx, static_cast<uint32_t>(k_idx), static_cast<uint32_t>(num_kb), e);
+            else store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, m_idx, k_idx, __uint_as_float(e << 23));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = r_base + 32 * k;
+        if (col_ok && r < valid_rows) {
+            const int m = exp_max[(r / p.out_bm) * ncb + cb];
+            const uint32_t e_out = m >= 6 ? m - 6 : 0;
+            const float rel = __uint_as_float((e_in[k] - e_out + 127u) << 23);  // 2^(e_in - e_out)
+            float v[16];
+            QuantSource<TKQ_FMT_E2M1>::unpack(raw[k], v, rel);
+            stg128(p.in.out + (row0 + r) * hidden + col0 + c16 * 16, cvt_e4m3x4(v[0], v[1], v[2], v[3]), cvt_e4m3x4(v[4], v[5], v[6], v[7]),
+                   cvt_e4m3x4(v[8], v[9], v[10], v[11]), cvt_e4m3x4(v[12], v[13], v[14], v[15]));
+        }
+    }
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
 static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
@@ -839,4 +911,44 @@ extern "C" int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t nu
         else swiglu_per_channel_cast_kernel<32, false><<<grid, kTileThreads, 0, s>>>(p);
     }
     return check_launch("swiglu_forward_and_per_channel_cast_and_transpose");
+}
+
+extern "C" int tkq_per_block_cast_lossless(const void* x, const void* x_sf, unsigned x_sf_flags, int64_t x_sf_stride, int x_block_m,
+                                           int x_block_k, int64_t num_tokens, int64_t hidden, int64_t x_row_stride, int out_block_m,
+                                           int out_block_k, unsigned flags, void* out, void* sf, int64_t sf_stride, void* stream) {
+    if (num_tokens < 0 || hidden <= 0 || x_row_stride < hidden || x_block_m <= 0 || x_block_k <= 0)
+        return set_error(TKQ_E_BAD_ARG, "per_block_cast_lossless: bad size");
+    if (num_tokens == 0) return 0;
+    if (x == nullptr || x_sf == nullptr || sf == nullptr || out == nullptr) return set_error(TKQ_E_BAD_ARG, "per_block_cast_lossless: null pointer");
+    if (((flags & TKQ_SF_UE8M0) && !(flags & TKQ_SF_COL_MAJOR)) || ((x_sf_flags & TKQ_SF_UE8M0) && !(x_sf_flags & TKQ_SF_COL_MAJOR)))
+        return set_error(TKQ_E_UNSUPPORTED, "packed ue8m0 scales need the column-major layout");
+    const bool bm_ok = out_block_m == 1 || out_block_m == 32 || out_block_m == 128;
+    const bool bk_ok = out_block_k == 32 || out_block_k == 128;
+    if (!bm_ok || !bk_ok || out_block_m % x_block_m != 0 || out_block_k % x_block_k != 0 || x_block_k % 16 != 0 || hidden % 32 != 0)
+        return set_error(TKQ_E_UNSUPPORTED,
+                         "per_block_cast_lossless: output blocks (1|32|128) x (32|128), multiples of the input block; hidden % 32 == 0");
+    if (reinterpret_cast<uintptr_t>(x) % 8 != 0 || (x_row_stride / 2) % 8 != 0 || !aligned16(out) ||
+        (reinterpret_cast<uintptr_t>(sf) & 3u) || (reinterpret_cast<uintptr_t>(x_sf) & 3u) || ((flags & TKQ_SF_UE8M0) && (sf_stride & 3)))
+        return set_error(TKQ_E_ALIGNMENT, "per_block_cast_lossless: x rows 8-byte aligned, out 16-byte aligned, scales 4-byte aligned");
+    LosslessParams p{};
+    p.in.x = x;
+    p.in.out = static_cast<uint8_t*>(out);
+    p.in.x_stride = x_row_stride;
+    p.in.num_tokens = num_tokens;
+    p.in.hidden = hidden;
+    p.in.in_sf = x_sf;
+    p.in.in_sf_stride = x_sf_stride;
+    p.in.in_sf_flags = x_sf_flags;
+    p.in.in_block_m = static_cast<uint32_t>(x_block_m);
+    p.in.in_block_k = static_cast<uint32_t>(x_block_k);
+    p.sf = sf;
+    p.sf_stride = sf_stride;
+    p.out_bm = static_cast<uint32_t>(out_block_m);
+    p.out_bk = static_cast<uint32_t>(out_block_k);
+    p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
+    p.flags = flags;
+    const int64_t tiles = ((num_tokens + kTile - 1) / kTile) * p.tiles_k;
+    if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
+    per_block_cast_lossless_kernel<<<static_cast<unsigned>(tiles), kTileThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("per_block_cast_lossless");
 }

@@ -6,6 +6,7 @@ _lib_module.lib()  # fail at import, not at first call, when the CUDA library is
 from .cast_back_e5m6_kernel import cast_back_e5m6  # noqa: E402
 from .cast_back_kernel import cast_back, per_token_cast_back  # noqa: E402
 from .common import unpack_from_e2m1fn_x2  # noqa: E402
+from .per_block_cast_lossless_kernel import per_block_cast_lossless  # noqa: E402
 from .per_block_cast_kernel import per_block_cast, per_block_cast_with_precomputed_sf, per_block_cast_with_sf_only  # noqa: E402
 from .per_channel_cast_and_transpose_kernel import per_channel_cast_and_transpose  # noqa: E402
 from .per_channel_cast_fused_kernel import per_channel_cast_fused  # noqa: E402
