@@ -181,6 +181,17 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
     gather = torch.randint(0, 7168, (8192,), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
     gather[::11] = -1
     gather = gather.to(device)
+
+    def backward_inputs(x):
+        rows, hidden = x.shape[0], x.shape[1] // 2
+        g = torch.Generator().manual_seed(11)
+        grad_out = torch.randn((rows, hidden), generator=g).to(torch.bfloat16).to(device)
+        weight = torch.rand((rows // 8, 8), generator=g).to(device)
+        pos = torch.randperm(rows, generator=g).to(torch.int32)
+        token_topk_to_pos = torch.empty(rows, dtype=torch.int32)
+        token_topk_to_pos[pos.long()] = torch.arange(rows, dtype=torch.int32)
+        return (quant.per_token_cast(x, 'e4m3', 128), grad_out, weight, pos.to(device), token_topk_to_pos.view(-1, 8).to(device))
+
     # the rows next to the hot path (dequantisation, re-quantisation, fused / transposing per-channel casts):
     # `prepare` turns the bf16 workload tensor into the op's input
     specs += [
@@ -193,6 +204,8 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         ('cfg2 per_channel_cast_fused bf16 + gather of 8192 rows [7168,2048]', 'cfg2', None,
          lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gather)),
         ('cfg2 per_channel_cast_and_transpose 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128)),
+        ('cfg3 swiglu_backward_and_per_token_cast g128 round_sf [16384,4096] (8 experts per token, every pair routed)', 'cfg3',
+         backward_inputs, lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
     ]
 
     def clone(v):

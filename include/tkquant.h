@@ -246,6 +246,36 @@ int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype, int64_t n
                                           long long* clamped_count, float sf_clamp_min, int num_sms, unsigned flags,
                                           void* out, void* sf, int64_t sf_stride, void* stream);
 
+/*
+ * SwiGLU backward fused with the per-token e4m3 cast of the input gradient.
+ * Replaces the launch in tile_kernels/quant/swiglu_backward_and_per_token_cast_kernel.py:235-236
+ * (kernel :34-152).  With g = x[:, :hidden] * x_sf, u = x[:, hidden:] * x_sf, d = grad_out, w = the row's
+ * routing weight (0 for a negative position), t = 1 + exp(-g), a = g / t * u, s = 1 / t, q = d * w * s:
+ *   out = a * w;   x_grad = [q * u * fma(g, 1 - s, 1),  q * g]  (0 where the forward clamp was active);
+ *   weight_grad[pos_to_token_topk[row]] = sum(d * a);  weight_grad[e] = 0 where token_topk_to_pos[e] == -1.
+ *
+ *   x                  [num_expand_tokens, 2 * hidden] e4m3, contiguous, hidden % num_per_channels == 0
+ *   x_sf               [num_expand_tokens, 2 * hidden / num_per_channels] fp32, contiguous
+ *   grad_out           [num_expand_tokens, hidden] bf16, contiguous
+ *   weight             [num_tokens, num_topk] fp32, contiguous
+ *   pos_to_token_topk  int32[num_expand_tokens], flat (token * num_topk + k) index or negative
+ *   token_topk_to_pos  int32[num_tokens, num_topk], row of x or -1
+ *   num_per_channels   32 or 128
+ *   swiglu_clamp       < 0: no clamp; else g = min(g, c), u = clamp(u, -c, c)
+ *   flags              TKQ_ROUND_SF only
+ *   out                [num_expand_tokens, hidden] bf16
+ *   x_grad_fp8         [num_expand_tokens, 2 * hidden] e4m3;  x_grad_sf  fp32, the shape of x_sf
+ *   x_grad             [num_expand_tokens, 2 * hidden] bf16
+ *   weight_grad        [num_tokens, num_topk] fp32
+ * num_expand_tokens == 0 launches nothing (weight_grad is left untouched, as in the reference).
+ */
+int tkq_swiglu_backward_and_per_token_cast(const void* x, const float* x_sf, const void* grad_out, const float* weight,
+                                           const int32_t* pos_to_token_topk, const int32_t* token_topk_to_pos,
+                                           int64_t num_expand_tokens, int64_t hidden, int64_t num_tokens, int64_t num_topk,
+                                           int64_t num_per_channels, float swiglu_clamp, unsigned flags, void* out,
+                                           void* x_grad_fp8, float* x_grad_sf, void* x_grad, float* weight_grad,
+                                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -251,6 +251,33 @@ def swiglu_forward(x: torch.Tensor, pos_to_token_topk: Optional[torch.Tensor] = 
     return y
 
 
+def swiglu_backward(x, grad_out: torch.Tensor, weight: torch.Tensor, pos_to_token_topk: torch.Tensor,
+                    token_topk_to_pos: torch.Tensor, num_per_channels: int,
+                    swiglu_clamp_value: Optional[float] = None):
+    """Same contract as tile_kernels.torch.swiglu_backward (swiglu.py:98-226): returns fp32 (out, x_grad_full,
+    weight_grad).  exp() is tkq_expf; the row sums of weight_grad are accumulated in double."""
+    assert num_per_channels in (32, 128)
+    data, _ = x
+    assert data.shape[-1] % (2 * num_per_channels) == 0
+    H = data.shape[-1] // 2
+    xf = cast_back((data.view(-1, 2 * H), x[1]), 'fp32', (1, num_per_channels)).contiguous()
+    T = xf.shape[0]
+    g = grad_out.view(-1, H).contiguous()
+    assert g.dtype == torch.bfloat16 and g.shape == (T, H)
+    w = weight.to(torch.float32).contiguous()
+    assert w.shape == token_topk_to_pos.shape
+    pos = pos_to_token_topk.to(torch.int32).contiguous()
+    out = torch.empty((T, H), dtype=torch.float32)
+    x_grad = torch.empty((T, 2 * H), dtype=torch.float32)
+    weight_grad = torch.zeros_like(w)
+    if T > 0:
+        lib().tkqo_swiglu_backward(_vp(xf.data_ptr()), _vp(g.data_ptr()), _i64(T), _i64(H),
+                                   ctypes.c_float(-1.0 if swiglu_clamp_value is None else swiglu_clamp_value),
+                                   _vp(pos.data_ptr()), _vp(w.data_ptr()), _vp(out.data_ptr()), _vp(x_grad.data_ptr()),
+                                   _vp(weight_grad.data_ptr()))
+    return out, x_grad, weight_grad
+
+
 def expf(x: torch.Tensor) -> torch.Tensor:
     x = x.contiguous().float()
     y = torch.empty_like(x)

@@ -14,6 +14,7 @@
  *   tile_kernels/torch/cast_e5m6.py:65-100   12-bit rounding + 8-in-3-words packing
  *   tile_kernels/torch/cast_e5m6.py:135-218  cast_to_e5m6()    -> tkqo_cast_e5m6
  *   tile_kernels/torch/swiglu.py:47-88       swiglu_forward()  -> tkqo_swiglu_forward
+ *   tile_kernels/torch/swiglu.py:98-226      swiglu_backward() -> tkqo_swiglu_backward
  *
  * The scale-factor *layouts* (column-major, packed ue8m0) are produced by the
  * numpy wrapper next to this file; this file always emits row-major fp32 scale
@@ -351,6 +352,53 @@ int tkqo_swiglu_forward(const void* x, int in_dtype, int64_t T, int64_t H, float
         counts[0] += c0;
         counts[1] += c1;
         counts[2] += c2;
+    }
+    return 0;
+}
+
+/*
+ * tkqo_swiglu_backward (swiglu.py:152-226), on the already dequantised input x[T, 2H] (fp32) and the bf16
+ * gradient d[T, H].  With g / u the two halves of a row, w the row's routing weight (0 for a negative
+ * position), t = 1 + exp(-g), a = g / t * u, s = 1 / t, q = d * w * s:
+ *   out[T, H]      = a * w
+ *   x_grad[T, 2H]  = [q * u * fma(g, 1 - s, 1), q * g], 0 where the clamp was active (swiglu.py:200-211;
+ *                    the fused multiply-add is the one elementwise_fma, swiglu.py:91-95, asks for)
+ *   weight_grad[pos_to_token_topk[r]] = sum_c d * a   (summed in double; entries without a row keep the
+ *                    caller's initial value, which the numpy wrapper sets to 0 as swiglu.py:217 does)
+ *   clamp < 0 disables the clamp
+ */
+int tkqo_swiglu_backward(const float* x, const uint16_t* grad_out, int64_t T, int64_t H, float clamp,
+                         const int32_t* pos_to_token_topk, const float* weight, float* out, float* x_grad,
+                         float* weight_grad) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < T; ++r) {
+        const int32_t index = pos_to_token_topk[r];
+        const float w = index >= 0 ? weight[index] : 0.0f;
+        double acc = 0.0;
+        for (int64_t c = 0; c < H; ++c) {
+            float g = x[r * 2 * H + c];
+            float u = x[r * 2 * H + H + c];
+            int clamped_g = 0, clamped_u = 0;
+            if (clamp >= 0.0f) {
+                clamped_g = g > clamp;
+                clamped_u = u > clamp || u < -clamp;
+                if (g > clamp) g = clamp;
+                if (u > clamp) u = clamp;
+                if (u < -clamp) u = -clamp;
+            }
+            const float d = u2f((uint32_t)grad_out[r * H + c] << 16);
+            const float t = 1.0f + tkq_expf(-g);
+            const float a = g / t * u;
+            acc += (double)(d * a);
+            const float s = 1.0f / t;
+            const float q = d * w * s;
+            out[r * H + c] = a * w;
+            const float vg = q * u * fmaf(g, 1.0f - s, 1.0f);
+            const float vu = q * g;
+            x_grad[r * 2 * H + c] = clamped_g ? 0.0f : vg;
+            x_grad[r * 2 * H + H + c] = clamped_u ? 0.0f : vu;
+        }
+        if (index >= 0) weight_grad[index] = (float)acc;
     }
     return 0;
 }

@@ -16,6 +16,8 @@ import json
 import os
 import sys
 
+os.environ.setdefault('TORCHDYNAMO_DISABLE', '1')  # see gen_swiglu_backward
+
 import numpy as np
 import torch
 
@@ -237,6 +239,57 @@ def gen_cast_back() -> None:
     np.savez_compressed(os.path.join(HERE, 'cast_back.npz'), **store)
 
 
+def gen_swiglu_backward() -> None:
+    """Reference outputs of swiglu_backward followed by cast (reference: tile_kernels/torch/swiglu.py:98-226, the
+    sequence of tests/quant/test_swiglu_backward_and_per_token_cast.py:83-102).
+
+    The reference routes 1 + x * (1 - s) through a torch.compile'd helper so that it becomes ONE fused
+    multiply-add (swiglu.py:91-95).  torch.compile has no working C++ back end in the container this runs in,
+    so the script is run with TORCHDYNAMO_DISABLE=1 and that helper is replaced by an exact emulation of the
+    fused operation: the product of two floats is exact in double, the sum is rounded once to double and once
+    to float."""
+    import tile_kernels.torch.swiglu as ref_swiglu
+
+    def fma(a, b, c):
+        return (a.double() * (b.double() if torch.is_tensor(b) else b) + c).float()
+
+    ref_swiglu.elementwise_fma = fma
+    store = {}
+    g = torch.Generator().manual_seed(4242)
+    T, H, num_tokens, topk = 24, 384, 8, 4
+    x = (torch.randn((T, 2 * H), generator=g) * 2).to(torch.bfloat16)
+    x[3] = 0
+    x[4] *= 40                      # saturated gates: exp under- and overflows, s = 0 or 1
+    d = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    w = torch.rand((num_tokens, topk), generator=g)
+    perm = torch.randperm(num_tokens * topk, generator=g)[:T].to(torch.int32)
+    perm[::9] = -1                  # unused expanded positions
+    t2p = torch.full((num_tokens * topk,), -1, dtype=torch.int32)
+    for row, index in enumerate(perm.tolist()):
+        if index >= 0:
+            t2p[index] = row
+    t2p = t2p.view(num_tokens, topk)
+    put(store, 'grad_out', d)
+    put(store, 'weight', w)
+    put(store, 'pos_to_token_topk', perm)
+    put(store, 'token_topk_to_pos', t2p)
+    for G in (32, 128):
+        q, qsf = cast(x, 'e4m3', (1, G))
+        put(store, f'g{G}/q', q)
+        put(store, f'g{G}/qsf', qsf)
+        for clamp in (None, 10.0, 0.5):
+            out, x_grad, w_grad = ref_swiglu.swiglu_backward((q, qsf), d, w, perm, t2p, G, clamp)
+            key = f'g{G}/c{clamp}'
+            put(store, key + '/out', out.to(torch.bfloat16))
+            put(store, key + '/x_grad', x_grad.to(torch.bfloat16))
+            put(store, key + '/weight_grad', w_grad)
+            for rnd in (False, True):
+                o8, s8 = cast(x_grad, 'e4m3', (1, G), round_sf=rnd)
+                put(store, f'{key}/r{int(rnd)}/fp8', o8)
+                put(store, f'{key}/r{int(rnd)}/sf', s8)
+    np.savez_compressed(os.path.join(HERE, 'swiglu_backward.npz'), **store)
+
+
 def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(raw(t).tobytes()).hexdigest()
 
@@ -265,12 +318,9 @@ def gen_config_digests() -> None:
 
 if __name__ == '__main__':
     torch.set_num_threads(8)
-    gen_cast()
-    gen_e5m6()
-    gen_e2m1_kat()
-    gen_swiglu()
-    gen_requant()
-    gen_cast_back()
-    gen_config_digests()
+    generators = {'cast': gen_cast, 'e5m6': gen_e5m6, 'e2m1_kat': gen_e2m1_kat, 'swiglu': gen_swiglu, 'requant': gen_requant,
+                  'cast_back': gen_cast_back, 'swiglu_backward': gen_swiglu_backward, 'config_digests': gen_config_digests}
+    for name in (sys.argv[1:] or list(generators)):   # optional arguments: the fixtures to (re)generate
+        generators[name]()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -29,6 +29,8 @@ SIGNATURES = {
     'tkq_cast_back': [_vp, _int, _vp, _uint, _i64, _int, _int, _i64, _i64, _int, _vp, _vp],
     'tkq_swiglu_forward_and_per_token_cast': [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _f32, _vp, _f32, _int, _uint,
                                               _vp, _vp, _i64, _vp],
+    'tkq_swiglu_backward_and_per_token_cast': [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _uint,
+                                               _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
 _lib = None

@@ -1,0 +1,235 @@
+// SwiGLU backward fused with the per-token e4m3 cast of the input gradient
+// (reference: tile_kernels/quant/swiglu_backward_and_per_token_cast_kernel.py:16-155; oracle form
+//  tile_kernels/torch/swiglu.py:98-226).
+//
+// Per expanded token (row) with gate part g = fp8(x[:, :H]) * sf and linear part u = fp8(x[:, H:]) * sf, incoming
+// gradient d (bf16) and routing weight w (0 for an unused position):
+//     t   = 1 + exp(-g)          a = g / t * u        s = 1 / t        q = d * w * s
+//     out = a * w                                       (bf16)
+//     dg  = q * u * fma(g, 1 - s, 1)    du = q * g      (0 where the forward clamp was active)
+//     x_grad = [dg, du]                                 (bf16, and e4m3 with one scale per G = 32 / 128 values)
+//     weight_grad[token, k] = sum over the row of d * a (0 where the (token, k) pair has no position)
+//
+// One warp owns a row: it walks the row in 512-column steps (a lane owns 16 consecutive columns of the gate
+// half and the same 16 of the linear half), keeps the row's dot product in registers and writes it once.
+// Every product is rounded separately (fp32, no contraction) except the one fused multiply-add the reference
+// asks for; exp is the reproducible routine shared with the CPU oracle.
+#include <cuda_bf16.h>
+
+#include "tkq_launch.cuh"
+#include "tkq_token_kernels.cuh"
+
+namespace tkq {
+
+struct SwigluBackwardParams {
+    const uint8_t* x;          // [rows, 2 * hidden] e4m3
+    const float* x_sf;         // [rows, 2 * hidden / G]
+    const uint8_t* grad_out;   // [rows, hidden] bf16
+    const float* weight;       // [tokens * topk]
+    const int32_t* pos_to_token_topk;  // [rows]
+    const int32_t* token_topk_to_pos;  // [tokens * topk]
+    uint8_t* out;              // [rows, hidden] bf16
+    uint8_t* x_grad_fp8;       // [rows, 2 * hidden] e4m3
+    float* x_grad_sf;          // [rows, 2 * hidden / G]
+    uint8_t* x_grad;           // [rows, 2 * hidden] bf16
+    float* weight_grad;        // [tokens * topk]
+    uint32_t rows;
+    uint32_t hidden;
+    uint32_t steps;            // ceil(hidden / 512)
+    uint32_t entries;          // tokens * topk
+    float swiglu_clamp;
+    float clamp_min;
+    bool round_sf;
+    bool fast_pow2;
+    bool wide;                 // grad_out, out and x_grad are 32-byte aligned: 256-bit accesses
+};
+
+constexpr int kBackwardThreads = 256;
+
+__device__ __forceinline__ void load_bf16x16(const uint8_t* p, bool wide, uint32_t* w) {
+    if (wide) {
+        const U32x8 a = ldg256(p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = a.v[i];
+    } else {
+        const U32x4 a = ldg128(p), b = ldg128(p + 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w[i] = a.v[i];
+            w[4 + i] = b.v[i];
+        }
+    }
+}
+
+__device__ __forceinline__ void store_bf16x16(uint8_t* p, bool wide, const float* v) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    if (wide) {
+        stg256(p, w);
+    } else {
+        stg128(p, w[0], w[1], w[2], w[3]);
+        stg128(p + 16, w[4], w[5], w[6], w[7]);
+    }
+}
+
+template <int LPG>
+__device__ __forceinline__ float group_max(float m) {
+#pragma unroll
+    for (int o = 1; o < LPG; o *= 2) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    return m;
+}
+
+// G = 16 * LPG values per scale
+template <int LPG, bool kClamp>
+__global__ void __launch_bounds__(kBackwardThreads) swiglu_backward_kernel(const SwigluBackwardParams p) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t nthreads = gridDim.x * blockDim.x;
+    const uint32_t hidden = p.hidden;
+    const uint32_t groups_per_half = hidden / (16u * LPG);
+
+    // (token, k) pairs that were routed nowhere get a zero gradient
+    for (uint32_t e = tid; e < p.entries; e += nthreads)
+        if (p.token_topk_to_pos[e] == -1) p.weight_grad[e] = 0.0f;
+
+    for (uint32_t row = tid >> 5; row < p.rows; row += nthreads >> 5) {
+        const int32_t index = p.pos_to_token_topk[row];
+        const float w = index >= 0 ? p.weight[index] : 0.0f;
+        const uint8_t* x_row = p.x + static_cast<int64_t>(row) * 2 * hidden;
+        const float* sf_row = p.x_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
+        float* out_sf_row = p.x_grad_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
+        float acc = 0.0f;
+        for (uint32_t step = 0; step < p.steps; ++step) {
+            const uint32_t col = step * 512u + lane * 16u;
+            const bool active = col < hidden;  // whole scale groups are active or not: hidden is a multiple of G
+            const uint32_t group = col / (16u * LPG);
+            QuantSource<TKQ_FMT_E4M3>::Raw raw_g, raw_u;
+            QuantSource<TKQ_FMT_E4M3>::zero(raw_g);
+            QuantSource<TKQ_FMT_E4M3>::zero(raw_u);
+            uint32_t raw_d[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            float sf_g = 0.0f, sf_u = 0.0f;
+            if (active) {
+                QuantSource<TKQ_FMT_E4M3>::issue(raw_g, x_row + col, false);
+                QuantSource<TKQ_FMT_E4M3>::issue(raw_u, x_row + hidden + col, false);
+                load_bf16x16(p.grad_out + (static_cast<int64_t>(row) * hidden + col) * 2, p.wide, raw_d);
+                sf_g = __ldg(sf_row + group);
+                sf_u = __ldg(sf_row + groups_per_half + group);
+            }
+            float g[16], u[16];
+            QuantSource<TKQ_FMT_E4M3>::unpack(raw_g, g, sf_g);
+            QuantSource<TKQ_FMT_E4M3>::unpack(raw_u, u, sf_u);
+            float dg[16], du[16], o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float gi = g[i], ui = u[i];
+                bool clamped_g = false, clamped_u = false;
+                if constexpr (kClamp) {
+                    clamped_g = gi > p.swiglu_clamp;
+                    clamped_u = ui > p.swiglu_clamp || ui < -p.swiglu_clamp;
+                    gi = clamped_g ? p.swiglu_clamp : gi;
+                    ui = ui > p.swiglu_clamp ? p.swiglu_clamp : ui;
+                    ui = ui < -p.swiglu_clamp ? -p.swiglu_clamp : ui;
+                }
+                const float d = (i & 1) ? bf16_hi(raw_d[i >> 1]) : bf16_lo(raw_d[i >> 1]);
+                const float t = __fadd_rn(1.0f, tkq_expf(-gi));
+                const float a = __fmul_rn(__fdiv_rn(gi, t), ui);
+                acc = __fadd_rn(acc, __fmul_rn(d, a));
+                const float s = __fdiv_rn(1.0f, t);
+                const float q = __fmul_rn(__fmul_rn(d, w), s);
+                o[i] = __fmul_rn(a, w);
+                const float vg = __fmul_rn(__fmul_rn(q, ui), __fmaf_rn(gi, __fsub_rn(1.0f, s), 1.0f));
+                const float vu = __fmul_rn(q, gi);
+                dg[i] = clamped_g ? 0.0f : vg;
+                du[i] = clamped_u ? 0.0f : vu;
+            }
+            const float amax_g = group_max<LPG>(absmax16(dg));
+            const float amax_u = group_max<LPG>(absmax16(du));
+            if (!active) continue;  // after the shuffles: the whole warp takes part in them
+            const Scale scale_g = make_scale_for<TKQ_FMT_E4M3>(amax_g, p.clamp_min, p.round_sf, p.fast_pow2);
+            const Scale scale_u = make_scale_for<TKQ_FMT_E4M3>(amax_u, p.clamp_min, p.round_sf, p.fast_pow2);
+            if (lane % LPG == 0) {
+                out_sf_row[group] = scale_g.sf;
+                out_sf_row[groups_per_half + group] = scale_u.sf;
+            }
+            const int64_t half_off = static_cast<int64_t>(row) * hidden + col;      // in [rows, hidden]
+            const int64_t full_off = static_cast<int64_t>(row) * 2 * hidden + col;  // in [rows, 2 * hidden]
+            store_bf16x16(p.out + half_off * 2, p.wide, o);
+            store_bf16x16(p.x_grad + full_off * 2, p.wide, dg);
+            store_bf16x16(p.x_grad + (full_off + hidden) * 2, p.wide, du);
+            quantize_store_e4m3x16(dg, scale_g.inv, p.x_grad_fp8 + full_off);
+            quantize_store_e4m3x16(du, scale_u.inv, p.x_grad_fp8 + full_off + hidden);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+        if (lane == 0 && index >= 0) p.weight_grad[index] = acc;
+    }
+}
+
+template <int LPG, bool kClamp>
+static int launch_backward(const SwigluBackwardParams& p, cudaStream_t stream) {
+    auto kernel = swiglu_backward_kernel<LPG, kClamp>;
+    constexpr int kWarps = kBackwardThreads / 32;
+    const int64_t blocks_of_work = std::max<int64_t>((static_cast<int64_t>(p.rows) + kWarps - 1) / kWarps,
+                                                     (static_cast<int64_t>(p.entries) + kBackwardThreads - 1) / kBackwardThreads);
+    const int grid = grid_size(kernel, kBackwardThreads, blocks_of_work, 0);
+    kernel<<<grid, kBackwardThreads, 0, stream>>>(p);
+    return check_launch("swiglu_backward_and_per_token_cast");
+}
+
+}  // namespace tkq
+
+using namespace tkq;
+
+extern "C" int tkq_swiglu_backward_and_per_token_cast(const void* x, const float* x_sf, const void* grad_out, const float* weight,
+                                                      const int32_t* pos_to_token_topk, const int32_t* token_topk_to_pos,
+                                                      int64_t num_expand_tokens, int64_t hidden, int64_t num_tokens,
+                                                      int64_t num_topk, int64_t num_per_channels, float swiglu_clamp,
+                                                      unsigned flags, void* out, void* x_grad_fp8, float* x_grad_sf,
+                                                      void* x_grad, float* weight_grad, void* stream) {
+    if (num_expand_tokens < 0 || hidden <= 0 || num_tokens < 0 || num_topk < 0)
+        return set_error(TKQ_E_BAD_ARG, "swiglu_backward_and_per_token_cast: bad size");
+    if (num_per_channels != 32 && num_per_channels != 128)
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu_backward_and_per_token_cast: num_per_channels must be 32 or 128");
+    if (hidden % num_per_channels != 0)
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu_backward_and_per_token_cast: hidden must be a multiple of num_per_channels");
+    if (flags & ~static_cast<unsigned>(TKQ_ROUND_SF))
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu_backward_and_per_token_cast: only TKQ_ROUND_SF applies (fp32 row-major scales)");
+    if (num_expand_tokens == 0) return 0;  // the reference launches nothing either: weight_grad stays as it was
+    if (!x || !x_sf || !grad_out || !weight || !pos_to_token_topk || !token_topk_to_pos || !out || !x_grad_fp8 || !x_grad_sf ||
+        !x_grad || !weight_grad)
+        return set_error(TKQ_E_BAD_ARG, "swiglu_backward_and_per_token_cast: null pointer");
+    if (num_expand_tokens >= (int64_t{1} << 31) || num_tokens * num_topk >= (int64_t{1} << 31) || hidden >= (int64_t{1} << 30))
+        return set_error(TKQ_E_UNSUPPORTED, "swiglu_backward_and_per_token_cast: more than 2^31 rows or routing entries");
+    if (!aligned16(x) || !aligned16(grad_out) || !aligned16(out) || !aligned16(x_grad_fp8) || !aligned16(x_grad))
+        return set_error(TKQ_E_ALIGNMENT, "swiglu_backward_and_per_token_cast: tensors must be 16-byte aligned");
+    SwigluBackwardParams p{};
+    p.x = static_cast<const uint8_t*>(x);
+    p.x_sf = x_sf;
+    p.grad_out = static_cast<const uint8_t*>(grad_out);
+    p.weight = weight;
+    p.pos_to_token_topk = pos_to_token_topk;
+    p.token_topk_to_pos = token_topk_to_pos;
+    p.out = static_cast<uint8_t*>(out);
+    p.x_grad_fp8 = static_cast<uint8_t*>(x_grad_fp8);
+    p.x_grad_sf = x_grad_sf;
+    p.x_grad = static_cast<uint8_t*>(x_grad);
+    p.weight_grad = weight_grad;
+    p.rows = static_cast<uint32_t>(num_expand_tokens);
+    p.hidden = static_cast<uint32_t>(hidden);
+    p.steps = static_cast<uint32_t>((hidden + 511) / 512);
+    p.entries = static_cast<uint32_t>(num_tokens * num_topk);
+    p.swiglu_clamp = swiglu_clamp;
+    p.clamp_min = 1e-4f;
+    p.round_sf = (flags & TKQ_ROUND_SF) != 0;
+    p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 448.0f);
+    auto aligned32 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 32 == 0; };
+    p.wide = aligned32(grad_out) && aligned32(out) && aligned32(x_grad);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool clamp = swiglu_clamp >= 0.0f;
+    if (num_per_channels == 128) return clamp ? launch_backward<8, true>(p, s) : launch_backward<8, false>(p, s);
+    return clamp ? launch_backward<2, true>(p, s) : launch_backward<2, false>(p, s);
+}

@@ -13,6 +13,7 @@ from .per_channel_cast_fused_kernel import per_channel_cast_fused  # noqa: E402
 from .per_channel_cast_kernel import per_channel_cast  # noqa: E402
 from .per_token_cast_kernel import per_token_cast, per_token_cast_with_precomputed_sf, per_token_cast_with_sf_only  # noqa: E402
 from .per_token_cast_to_e5m6_kernel import per_token_cast_to_e5m6  # noqa: E402
+from .swiglu_backward_and_per_token_cast_kernel import swiglu_backward_and_per_token_cast  # noqa: E402
 from .swiglu_forward_and_per_channel_cast_and_transpose_kernel import swiglu_forward_and_per_channel_cast_and_transpose  # noqa: E402
 from .swiglu_forward_and_per_token_cast_kernel import swiglu_forward_and_per_token_cast  # noqa: E402
 from .types import QuantTensor  # noqa: E402

@@ -4,7 +4,8 @@
     python -m tilekernels_b200.testing.run_case --op cfg5 --rows 32768 --launches 3
 
 ops: cfg1 (per-token e4m3, fp32 scales), cfg2_block, cfg2_channel, cfg3 (SwiGLU + cast), cfg4_fp4, cfg4_e5m6,
-cfg5 (per-token e4m3, ue8m0 scales).  --rows limits the row count (same per-row distribution).
+cfg5 (per-token e4m3, ue8m0 scales), back_e4m3 / back_e5m6 (dequantisation of cfg4's tensor to bf16).  --rows limits
+the row count (same per-row distribution).
 """
 import argparse
 
@@ -20,6 +21,8 @@ OPS = {
     'cfg3': ('cfg3', lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128)),
     'cfg4_fp4': ('cfg4', lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)),
     'cfg4_e5m6': ('cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
+    'back_e4m3': ('cfg4', lambda q: (quant.cast_back(q, 'bf16', (1, 128)),)),
+    'back_e5m6': ('cfg4', lambda q: (quant.cast_back_e5m6(q, 'bf16', (1, q[0].shape[1] // 3 * 2)),)),
     'cfg5': ('cfg5', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, True, True, True)),
 }
 
@@ -32,6 +35,10 @@ def main() -> None:
     args = ap.parse_args()
     cfg, op = OPS[args.op]
     x = make_config_input(cfg, args.rows).cuda()
+    if args.op == 'back_e4m3':
+        x = quant.per_token_cast(x, 'e4m3', 128)
+    elif args.op == 'back_e5m6':
+        x = quant.per_token_cast(x, 'e5m6', x.shape[1])
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for i in range(args.launches):
         if i == args.launches - 1:
@@ -39,9 +46,11 @@ def main() -> None:
         out = op(x)
     stop.record()
     torch.cuda.synchronize()
-    nbytes = x.numel() * x.element_size() + sum(t.numel() * t.element_size() for t in out)
+    tensors = (list(x) if isinstance(x, tuple) else [x]) + list(out)
+    nbytes = sum(t.numel() * t.element_size() for t in tensors)
+    rows = tensors[0].shape[0]
     us = start.elapsed_time(stop) * 1e3
-    print(f'{args.op}: rows={x.shape[0]} bytes={nbytes} last launch {us:.1f} us -> {nbytes / us / 1e3:.0f} GB/s (includes host launch overhead)')
+    print(f'{args.op}: rows={rows} bytes={nbytes} last launch {us:.1f} us -> {nbytes / us / 1e3:.0f} GB/s (includes host launch overhead)')
 
 
 if __name__ == '__main__':
