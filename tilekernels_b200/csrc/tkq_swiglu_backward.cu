@@ -45,6 +45,9 @@ struct SwigluBackwardParams {
 };
 
 constexpr int kBackwardThreads = 256;
+#ifndef TKQ_BW_MIN_BLOCKS
+#define TKQ_BW_MIN_BLOCKS 4
+#endif
 
 __device__ __forceinline__ void load_bf16x16(const uint8_t* p, bool wide, uint32_t* w) {
     if (wide) {
@@ -58,6 +61,15 @@ __device__ __forceinline__ void load_bf16x16(const uint8_t* p, bool wide, uint32
             w[i] = a.v[i];
             w[4 + i] = b.v[i];
         }
+    }
+}
+
+__device__ __forceinline__ void store_words8(uint8_t* p, bool wide, const uint32_t* w) {
+    if (wide) {
+        stg256(p, w);
+    } else {
+        stg128(p, w[0], w[1], w[2], w[3]);
+        stg128(p + 16, w[4], w[5], w[6], w[7]);
     }
 }
 
@@ -83,9 +95,61 @@ __device__ __forceinline__ float group_max(float m) {
     return m;
 }
 
+// The arithmetic of one lane's 16 columns.  kInRange: every gate is a bf16 number of magnitude in [2^-40, 44] below
+// the clamp, so exp needs no argument clamp and both quotients come from ONE refined reciprocal (the sequence
+// swiglu_bf16_in_range documents; for the numerator 1 and the 3-bit FP8 mantissas it was compared with IEEE
+// division for all 2^23 denominator mantissas of all 64 binades of [1, 2^64): no difference).
+template <bool kClamp, bool kInRange>
+__device__ __forceinline__ float backward_chunk(const float* g, const float* u, const uint32_t* raw_d, float w, float clamp,
+                                                float acc, float* dg, float* du, uint32_t* o) {
+    float o_even = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float gi = g[i], ui = u[i];
+        bool clamped_g = false, clamped_u = false;
+        if constexpr (kClamp) {
+            clamped_g = gi > clamp;
+            clamped_u = ui > clamp || ui < -clamp;
+            gi = clamped_g ? clamp : gi;
+            ui = ui > clamp ? clamp : ui;
+            ui = ui < -clamp ? -clamp : ui;
+        }
+        const float d = (i & 1) ? bf16_hi(raw_d[i >> 1]) : bf16_lo(raw_d[i >> 1]);
+        float ratio, s;  // g / t and 1 / t, both correctly rounded
+        if constexpr (kInRange) {
+            const float t = __fadd_rn(1.0f, tkq_expf_impl<false>(-gi));
+            float y;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(t));
+            y = __fmaf_rn(y, __fmaf_rn(-t, y, 1.0f), y);
+            s = __fmaf_rn(__fmaf_rn(-t, y, 1.0f), y, y);
+            const float q0 = __fmul_rn(gi, y);
+            ratio = __fmaf_rn(__fmaf_rn(-t, q0, gi), y, q0);
+        } else {
+            const float t = __fadd_rn(1.0f, tkq_expf(-gi));
+            ratio = __fdiv_rn(gi, t);
+            s = __fdiv_rn(1.0f, t);
+        }
+        const float a = __fmul_rn(ratio, ui);
+        acc = __fadd_rn(acc, __fmul_rn(d, a));
+        const float q = __fmul_rn(__fmul_rn(d, w), s);
+        const float oi = __fmul_rn(a, w);
+        if (i & 1) {  // the weighted activation leaves as bf16 pairs
+            const __nv_bfloat162 b = __floats2bfloat162_rn(o_even, oi);
+            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b);
+        } else {
+            o_even = oi;
+        }
+        const float vg = __fmul_rn(__fmul_rn(q, ui), __fmaf_rn(gi, __fsub_rn(1.0f, s), 1.0f));
+        const float vu = __fmul_rn(q, gi);
+        dg[i] = clamped_g ? 0.0f : vg;
+        du[i] = clamped_u ? 0.0f : vu;
+    }
+    return acc;
+}
+
 // G = 16 * LPG values per scale
 template <int LPG, bool kClamp>
-__global__ void __launch_bounds__(kBackwardThreads) swiglu_backward_kernel(const SwigluBackwardParams p) {
+__global__ void __launch_bounds__(kBackwardThreads, TKQ_BW_MIN_BLOCKS) swiglu_backward_kernel(const SwigluBackwardParams p) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t nthreads = gridDim.x * blockDim.x;
@@ -122,30 +186,22 @@ __global__ void __launch_bounds__(kBackwardThreads) swiglu_backward_kernel(const
             float g[16], u[16];
             QuantSource<TKQ_FMT_E4M3>::unpack(raw_g, g, sf_g);
             QuantSource<TKQ_FMT_E4M3>::unpack(raw_u, u, sf_u);
-            float dg[16], du[16], o[16];
+            float dg[16], du[16];
+            uint32_t o[8];
+            // chunks whose gates are bf16 numbers (an FP8 code times a power-of-two scale) of magnitude in
+            // [2^-40, 44], none clamped, take the cheaper evaluation
+            uint32_t low_bits = 0;
+            float g_min = g[0], g_max = g[0];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                float gi = g[i], ui = u[i];
-                bool clamped_g = false, clamped_u = false;
-                if constexpr (kClamp) {
-                    clamped_g = gi > p.swiglu_clamp;
-                    clamped_u = ui > p.swiglu_clamp || ui < -p.swiglu_clamp;
-                    gi = clamped_g ? p.swiglu_clamp : gi;
-                    ui = ui > p.swiglu_clamp ? p.swiglu_clamp : ui;
-                    ui = ui < -p.swiglu_clamp ? -p.swiglu_clamp : ui;
-                }
-                const float d = (i & 1) ? bf16_hi(raw_d[i >> 1]) : bf16_lo(raw_d[i >> 1]);
-                const float t = __fadd_rn(1.0f, tkq_expf(-gi));
-                const float a = __fmul_rn(__fdiv_rn(gi, t), ui);
-                acc = __fadd_rn(acc, __fmul_rn(d, a));
-                const float s = __fdiv_rn(1.0f, t);
-                const float q = __fmul_rn(__fmul_rn(d, w), s);
-                o[i] = __fmul_rn(a, w);
-                const float vg = __fmul_rn(__fmul_rn(q, ui), __fmaf_rn(gi, __fsub_rn(1.0f, s), 1.0f));
-                const float vu = __fmul_rn(q, gi);
-                dg[i] = clamped_g ? 0.0f : vg;
-                du[i] = clamped_u ? 0.0f : vu;
+            for (int i = 0; i < 16; i += 2) {
+                low_bits |= __float_as_uint(g[i]) | __float_as_uint(g[i + 1]);
+                g_min = min3_abs(g_min, g[i], g[i + 1]);
+                g_max = max3_abs(g_max, g[i], g[i + 1]);
             }
+            bool in_range = (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f && g_max <= 44.0f;
+            if constexpr (kClamp) in_range = in_range && g_max <= p.swiglu_clamp;
+            if (in_range) acc = backward_chunk<kClamp, true>(g, u, raw_d, w, p.swiglu_clamp, acc, dg, du, o);
+            else acc = backward_chunk<kClamp, false>(g, u, raw_d, w, p.swiglu_clamp, acc, dg, du, o);
             const float amax_g = group_max<LPG>(absmax16(dg));
             const float amax_u = group_max<LPG>(absmax16(du));
             if (!active) continue;  // after the shuffles: the whole warp takes part in them
@@ -157,7 +213,7 @@ __global__ void __launch_bounds__(kBackwardThreads) swiglu_backward_kernel(const
             }
             const int64_t half_off = static_cast<int64_t>(row) * hidden + col;      // in [rows, hidden]
             const int64_t full_off = static_cast<int64_t>(row) * 2 * hidden + col;  // in [rows, 2 * hidden]
-            store_bf16x16(p.out + half_off * 2, p.wide, o);
+            store_words8(p.out + half_off * 2, p.wide, o);
             store_bf16x16(p.x_grad + full_off * 2, p.wide, dg);
             store_bf16x16(p.x_grad + (full_off + hidden) * 2, p.wide, du);
             quantize_store_e4m3x16(dg, scale_g.inv, p.x_grad_fp8 + full_off);
