@@ -190,7 +190,7 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         pos = torch.randperm(rows, generator=g).to(torch.int32)
         token_topk_to_pos = torch.empty(rows, dtype=torch.int32)
         token_topk_to_pos[pos.long()] = torch.arange(rows, dtype=torch.int32)
-        return (quant.per_token_cast(x, 'e4m3', 128), grad_out, weight, pos.to(device), token_topk_to_pos.view(-1, 8).to(device))
+        return (quant.per_token_cast(x, 'e4m3', 128, round_sf=True), grad_out, weight, pos.to(device), token_topk_to_pos.view(-1, 8).to(device))
 
     # the rows next to the hot path (dequantisation, re-quantisation, fused / transposing per-channel casts):
     # `prepare` turns the bf16 workload tensor into the op's input
@@ -204,7 +204,7 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         ('cfg2 per_channel_cast_fused bf16 + gather of 8192 rows [7168,2048]', 'cfg2', None,
          lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gather)),
         ('cfg2 per_channel_cast_and_transpose 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128)),
-        ('cfg3 swiglu_backward_and_per_token_cast g128 round_sf [16384,4096] (8 experts per token, every pair routed)', 'cfg3',
+        ('cfg3 swiglu_backward_and_per_token_cast g128 round_sf, input scales powers of two [16384,4096]', 'cfg3',
          backward_inputs, lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
     ]
 
