@@ -276,6 +276,28 @@ int tkq_swiglu_backward_and_per_token_cast(const void* x, const float* x_sf, con
                                            void* x_grad_fp8, float* x_grad_sf, void* x_grad, float* weight_grad,
                                            void* stream);
 
+/*
+ * Expansion of token rows (and their scale factors) into the fused expert layout: out[pos] = x[t] for every
+ * pos = token_topk_to_pos[t, k] >= 0; rows with pos_to_expert[pos] < 0 are zero-filled; other rows are left alone.
+ * Replaces the launches in tile_kernels/moe/expand_to_fused_kernel.py:127-128 (expand_to_fused, x_sf = NULL) and
+ * :196-197 (expand_to_fused_with_sf); kernel :44-92.
+ *
+ *   x                  [num_tokens, row_bytes] bytes, contiguous (any element type), row_bytes % 16 == 0
+ *   x_sf, sf_words     optional [num_tokens, sf_words] 4-byte words (fp32 scales or packed ue8m0), contiguous;
+ *                      NULL and 0 for a plain expansion
+ *   token_topk_to_pos  int32[num_tokens, num_topk], expanded position or negative
+ *   pos_to_expert      int32[num_expanded_tokens], negative = padding row
+ *   flags              TKQ_SF_COL_MAJOR: out_sf is [sf_words, out_sf_stride] with one column per expanded row
+ *                      (the TMA-aligned layout, out_sf_stride = align(num_expanded_tokens, 4));
+ *                      else [num_expanded_tokens, out_sf_stride] row-major
+ *   out                [num_expanded_tokens, row_bytes]
+ * num_tokens == 0 launches nothing (padding rows are not cleared either, as in the reference).
+ */
+int tkq_expand_to_fused(const void* x, int64_t num_tokens, int64_t row_bytes, const void* x_sf, int64_t sf_words,
+                        const int32_t* token_topk_to_pos, int64_t num_topk, const int32_t* pos_to_expert,
+                        int64_t num_expanded_tokens, unsigned flags, void* out, void* out_sf, int64_t out_sf_stride,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,6 +12,7 @@ import ctypes
 import os
 from typing import Optional
 
+import numpy as np
 import torch
 
 from .build import LIB, build as build_library
@@ -276,6 +277,36 @@ def swiglu_backward(x, grad_out: torch.Tensor, weight: torch.Tensor, pos_to_toke
                                    _vp(pos.data_ptr()), _vp(w.data_ptr()), _vp(out.data_ptr()), _vp(x_grad.data_ptr()),
                                    _vp(weight_grad.data_ptr()))
     return out, x_grad, weight_grad
+
+
+def expand_to_fused(x: torch.Tensor, token_topk_to_pos: torch.Tensor, pos_to_expert: torch.Tensor) -> torch.Tensor:
+    """Row expansion (tile_kernels/torch/expand_to_fused.py:6-39): token t goes to every position
+    token_topk_to_pos[t, k] >= 0, every other row of the result is zero."""
+    num_expanded = pos_to_expert.shape[0]
+    dense = torch.empty(x.shape, dtype=x.dtype)
+    dense.copy_(x)
+    rows = dense.view(torch.uint8).numpy().reshape(x.shape[0], -1)
+    out = np.zeros((num_expanded, rows.shape[1]), dtype=np.uint8)
+    for t, positions in enumerate(token_topk_to_pos.tolist()):
+        for pos in positions:
+            if pos >= 0:
+                out[pos] = rows[t]
+    return torch.from_numpy(out).view(x.dtype).view(num_expanded, x.shape[1])
+
+
+def expand_to_fused_with_sf(x, num_per_channels: int, token_topk_to_pos: torch.Tensor, pos_to_expert: torch.Tensor,
+                            use_tma_aligned_col_major_sf: bool = False):
+    """Row expansion of data and scales (tile_kernels/torch/expand_to_fused.py:42-91); the scales of the result
+    are row-major, or a transposed view of a zero-initialised (hidden_sf, align(positions, 4)) buffer."""
+    data, sf = x
+    out = expand_to_fused(data, token_topk_to_pos, pos_to_expert)
+    out_sf_rows = expand_to_fused(sf, token_topk_to_pos, pos_to_expert)
+    if not use_tma_aligned_col_major_sf:
+        return out, out_sf_rows
+    num_expanded = pos_to_expert.shape[0]
+    storage = torch.zeros((sf.shape[1], _ceil_div(num_expanded, 4) * 4), dtype=sf.dtype)
+    storage[:, :num_expanded] = out_sf_rows.T
+    return out, storage[:, :num_expanded].T
 
 
 def expf(x: torch.Tensor) -> torch.Tensor:

@@ -290,6 +290,38 @@ def gen_swiglu_backward() -> None:
     np.savez_compressed(os.path.join(HERE, 'swiglu_backward.npz'), **store)
 
 
+def gen_expand() -> None:
+    """Row expansion into the fused expert layout (reference: tile_kernels/torch/expand_to_fused.py:6-91), plain and
+    with scale factors in the three layouts the reference's test uses."""
+    from tile_kernels.torch.expand_to_fused import expand_to_fused, expand_to_fused_with_sf
+    store = {}
+    g = torch.Generator().manual_seed(8642)
+    num_tokens, topk, hidden, num_expanded = 19, 3, 256, 70
+    x = torch.randn((num_tokens, hidden), generator=g).to(torch.bfloat16)
+    routed = torch.rand(num_tokens * topk, generator=g) > 0.25
+    positions = torch.randperm(num_expanded, generator=g)[:int(routed.sum())].to(torch.int32)
+    t2p = torch.full((num_tokens * topk,), -1, dtype=torch.int32)
+    t2p[routed] = positions
+    t2p = t2p.view(num_tokens, topk)
+    p2e = torch.full((num_expanded,), -1, dtype=torch.int32)
+    p2e[positions.long()] = torch.randint(0, 8, (positions.numel(),), generator=g, dtype=torch.int32)
+    put(store, 'x', x)
+    put(store, 'token_topk_to_pos', t2p)
+    put(store, 'pos_to_expert', p2e)
+    put(store, 'plain', expand_to_fused(x, t2p, p2e))
+    for G in (32, 128):
+        for col, rnd, ue in ((False, True, False), (True, True, False), (True, True, True)):
+            q, qsf = cast(x, 'e4m3', (1, G), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+            qsf = qsf.contiguous()
+            out, out_sf = expand_to_fused_with_sf((q, qsf), G, t2p, p2e, col)
+            key = f'g{G}/{int(col)}{int(rnd)}{int(ue)}'
+            put(store, key + '/q', q)
+            put(store, key + '/qsf', qsf)
+            put(store, key + '/out', out)
+            put(store, key + '/out_sf', out_sf)
+    np.savez_compressed(os.path.join(HERE, 'expand.npz'), **store)
+
+
 def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(raw(t).tobytes()).hexdigest()
 
@@ -319,7 +351,7 @@ def gen_config_digests() -> None:
 if __name__ == '__main__':
     torch.set_num_threads(8)
     generators = {'cast': gen_cast, 'e5m6': gen_e5m6, 'e2m1_kat': gen_e2m1_kat, 'swiglu': gen_swiglu, 'requant': gen_requant,
-                  'cast_back': gen_cast_back, 'swiglu_backward': gen_swiglu_backward, 'config_digests': gen_config_digests}
+                  'cast_back': gen_cast_back, 'swiglu_backward': gen_swiglu_backward, 'expand': gen_expand, 'config_digests': gen_config_digests}
     for name in (sys.argv[1:] or list(generators)):   # optional arguments: the fixtures to (re)generate
         generators[name]()
     for f in sorted(os.listdir(HERE)):

@@ -12,7 +12,7 @@ the library exists.
 import importlib
 
 __version__ = '0.1.0'
-_SUBMODULES = ('config', 'utils', 'quant', 'testing', 'host', 'sharding', 'build')
+_SUBMODULES = ('config', 'utils', 'quant', 'moe', 'testing', 'host', 'sharding', 'build')
 
 
 def __getattr__(name):

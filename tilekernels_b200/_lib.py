@@ -31,6 +31,7 @@ SIGNATURES = {
                                               _vp, _vp, _i64, _vp],
     'tkq_swiglu_backward_and_per_token_cast': [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _uint,
                                                _vp, _vp, _vp, _vp, _vp, _vp],
+    'tkq_expand_to_fused': [_vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _uint, _vp, _vp, _i64, _vp],
 }
 
 _lib = None

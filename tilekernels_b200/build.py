@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, 'csrc')
 INCLUDE = os.path.join(os.path.dirname(HERE), 'include')
 LIB_DIR = os.path.join(HERE, 'lib')
 LIB = os.path.join(LIB_DIR, 'libtkquant.so')
-SOURCES = ['tkq_api.cu', 'tkq_per_token.cu', 'tkq_swiglu.cu', 'tkq_tile.cu', 'tkq_cast_back.cu', 'tkq_swiglu_backward.cu']
+SOURCES = ['tkq_api.cu', 'tkq_per_token.cu', 'tkq_swiglu.cu', 'tkq_tile.cu', 'tkq_cast_back.cu', 'tkq_swiglu_backward.cu', 'tkq_expand.cu']
 NVCC_FLAGS = ['-O3', '-std=c++17', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-fmad=false',
               '-Xcompiler', '-fPIC', '-I' + INCLUDE, '-I' + CSRC]
 
