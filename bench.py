@@ -164,6 +164,7 @@ def time_graph(torch, op, inputs, launches: int, replays: int = 7):
 def bench_other_ops(torch, quant, device, count_bytes) -> list:
     """cfg1-cfg4 on one GPU.  Working sets below the L2 size are timed L2-cold: each launch uses the next of
     `sets` distinct input/output sets whose total size exceeds twice the L2."""
+    from tilekernels_b200 import moe
     from tilekernels_b200.testing import make_config_input
     peak, _ = hbm_peak()
     specs = [
@@ -192,6 +193,12 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         token_topk_to_pos[pos.long()] = torch.arange(rows, dtype=torch.int32)
         return (quant.per_token_cast(x, 'e4m3', 128, round_sf=True), grad_out, weight, pos.to(device), token_topk_to_pos.view(-1, 8).to(device))
 
+
+    def expand_inputs(x):
+        q, sf = quant.per_token_cast(x, 'e4m3', 128, None, **ue)
+        positions = torch.randperm(x.shape[0] * 8, generator=torch.Generator().manual_seed(13)).to(torch.int32)
+        return ((q, sf.contiguous()), positions.view(-1, 8).to(device), torch.zeros(x.shape[0] * 8, dtype=torch.int32, device=device))
+
     # the rows next to the hot path (dequantisation, re-quantisation, fused / transposing per-channel casts):
     # `prepare` turns the bf16 workload tensor into the op's input
     specs += [
@@ -206,6 +213,8 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         ('cfg2 per_channel_cast_and_transpose 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128)),
         ('cfg3 swiglu_backward_and_per_token_cast g128 round_sf, input scales powers of two [16384,4096]', 'cfg3',
          backward_inputs, lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
+        ('cfg1 moe.expand_to_fused_with_sf of the FP8 cast, 8 positions per token, ue8m0 scales [4096,7168] -> [32768,7168]', 'cfg1',
+         expand_inputs, lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True)),
     ]
 
     def clone(v):
