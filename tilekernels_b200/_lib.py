@@ -3,6 +3,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
+# TKQ_LIB_PATH points at another build of the library (e.g. one installed outside the package)
 LIB_PATH = os.environ.get('TKQ_LIB_PATH') or os.path.join(_HERE, 'lib', 'libtkquant.so')
 
 # enums of include/tkquant.h

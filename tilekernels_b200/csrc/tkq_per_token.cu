@@ -13,11 +13,8 @@ static int launch_group(const TokenCastParams& p, cudaStream_t stream) {
     // bytes per lane and step: 32 (bf16) or 64 (fp32)
     // measured on B200: many resident warps with one step each beat fewer warps with several steps in flight;
     // FP4 (half the output bytes per step) prefers two
-    const int u = group_unroll((DT == TKQ_DT_BF16 && FMT == TKQ_FMT_E2M1) ? 2 : 1, DT == TKQ_DT_BF16 ? 4 : 2);
-    if (u == 4) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, (DT == TKQ_DT_BF16 ? 4 : 2), 0>, p,
-                                           DT == TKQ_DT_BF16 ? 4 : 2, 0, stream, what);
-    if (u == 2) return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, 2, 0>, p, 2, 0, stream, what);
-    return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, 1, 0>, p, 1, 0, stream, what);
+    constexpr int kSteps = (DT == TKQ_DT_BF16 && FMT == TKQ_FMT_E2M1) ? 2 : 1;
+    return launch_group_kernel(group_cast_kernel<PlainSource<DT>, kSourcePlain, FMT, LPG, kSteps, 0>, p, kSteps, 0, stream, what);
 }
 
 template <int DT, int FMT>
@@ -80,7 +77,7 @@ static int dispatch_e5m6(const TokenCastParams& p, cudaStream_t stream) {
     int k = 0, threads = 0;
     constexpr int EB = DT == TKQ_DT_BF16 ? 2 : 4;
     const uint32_t stage_bytes = static_cast<uint32_t>((p.hidden * EB + 127) / 128 * 128);
-    if (p.hidden % 32 == 0 && stage_bytes <= 96 * 1024 && std::getenv("TKQ_E5M6_NO_PIPELINE") == nullptr) {
+    if (p.hidden % 32 == 0 && stage_bytes <= 96 * 1024) {
         // blocks of about 256 threads so that several blocks (and their rings) share an SM
         if (row_shape(p.hidden / 16, 256, &k, &threads)) {
             const uint32_t stages = stage_bytes <= 16 * 1024 ? 3u : 2u;

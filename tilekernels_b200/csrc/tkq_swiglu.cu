@@ -9,10 +9,7 @@ namespace tkq {
 template <int DT, int kClampMode>
 static int launch_swiglu_group(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
     const char* what = "swiglu_forward_and_per_token_cast (group kernel)";
-    // two input streams per step: 64 (bf16) or 128 (fp32) bytes per lane and step
-    const int u = group_unroll(1, DT == TKQ_DT_BF16 ? 2 : 1);
-    if (u == 2) return launch_group_kernel(group_cast_kernel<SwigluSource<DT>, kSourceSwiglu, TKQ_FMT_E4M3, 8, (DT == TKQ_DT_BF16 ? 2 : 1), kClampMode>,
-                                           p, DT == TKQ_DT_BF16 ? 2 : 1, sm_limit, stream, what);
+    // two input streams per step: 64 (bf16) or 128 (fp32) bytes per lane and step; one step per work item
     return launch_group_kernel(group_cast_kernel<SwigluSource<DT>, kSourceSwiglu, TKQ_FMT_E4M3, 8, 1, kClampMode>, p, 1, sm_limit, stream, what);
 }
 

@@ -252,35 +252,37 @@ template <int DT>
 __global__ void __launch_bounds__(kTileThreads) per_channel_cast_kernel(const __grid_constant__ CUtensorMap tmap, const TileParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[8];
-    __shared__ int col_amax_bits[2][kTile];
+    __shared__ __align__(16) float warp_max[kTileThreads / 32][kTile];  // column maxima of each warp's 16 rows
     __shared__ float col_inv[kTile];
 
-    const int t = threadIdx.x, lane = t & 31;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int c16 = t & 7, r_base = t >> 3;
     const bool round_sf = p.flags & TKQ_ROUND_SF;
-    (&col_amax_bits[0][0])[t] = 0;  // 256 threads, 2 x 128 entries
 
-    run_tile_pipeline<DT>(p, &tmap, smem, full_bar, [&](uint32_t i, const TileCoord& c, float (&v)[4][16], bool col_ok) {
-        int* col_amax = col_amax_bits[i & 1];
+    run_tile_pipeline<DT>(p, &tmap, smem, full_bar, [&](uint32_t, const TileCoord& c, float (&v)[4][16], bool col_ok) {
         float cm[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) cm[j] = max3_abs(fabsf(v[0][j]), v[1][j], max3_abs(0.0f, v[2][j], v[3][j]));
-        // combine the 4 rows a warp holds per chunk, then the 8 warps through shared-memory atomics
+        // combine the 4 row groups a warp holds per chunk by shuffles, then the 8 warps through shared memory
+        // (plain stores: every warp has its own row of warp_max)
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 8));
             cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 16));
         }
         if (lane < 8) {
+            float4* dst = reinterpret_cast<float4*>(&warp_max[warp][c16 * 16]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) atomicMax(&col_amax[c16 * 16 + j], __float_as_int(cm[j]));
+            for (int q = 0; q < 4; ++q) dst[q] = make_float4(cm[4 * q], cm[4 * q + 1], cm[4 * q + 2], cm[4 * q + 3]);
         }
         __syncthreads();
         if (t < kTile) {
-            const Scale s = make_scale_for<TKQ_FMT_E4M3>(__int_as_float(col_amax[t]), p.clamp_min, round_sf, p.fast_pow2);
+            float m = warp_max[0][t];
+#pragma unroll
+            for (int w = 1; w < kTileThreads / 32; ++w) m = fmaxf(m, warp_max[w][t]);
+            const Scale s = make_scale_for<TKQ_FMT_E4M3>(m, p.clamp_min, round_sf, p.fast_pow2);
             col_inv[t] = s.inv;
             if (t < c.valid_cols) static_cast<float*>(p.sf)[c.tile_m * p.hidden + c.col0 + t] = s.sf;
-            col_amax_bits[(i + 1) & 1][t] = 0;
         }
         __syncthreads();
         float inv[16];
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(kTileThreads) per_channel_cast_kernel(const __
 // as [hidden, num_tokens] (reference: tile_kernels/quant/per_channel_cast_and_transpose_kernel.py:85-123).
 // The tile is read from shared memory in the transposed sense: thread t owns channel t % 128 and the 64 tokens
 // (t / 128) * 64 ... of the tile, so a warp reads 64 contiguous bytes per token row (no bank conflicts), the
-// column maximum is mostly thread-local, and 16 consecutive tokens of a channel leave as one 128-bit store.
+// column maximum is mostly thread-local, and 32 consecutive tokens of a channel leave as one 256-bit store.
 // ---------------------------------------------------------------------------
 template <int NPT>
 __global__ void __launch_bounds__(kTileThreads) per_channel_cast_transpose_kernel(const __grid_constant__ CUtensorMap tmap,
@@ -356,18 +358,26 @@ __global__ void __launch_bounds__(kTileThreads) per_channel_cast_transpose_kerne
             }
             if (!ch_ok) return;
             uint8_t* dst = p.out + (c.col0 + ch) * p.num_tokens + c.row0 + half * 64;
+            // 16 tokens = 8 packed words -> 16 bytes; two such groups leave as ONE 256-bit store, so that every lane
+            // writes whole 32-byte sectors (lanes are num_tokens bytes apart: half-sector stores cost twice)
+            const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {  // 16 tokens = 8 packed words -> 16 bytes
-                if (half * 64 + g * 16 >= c.valid_rows) break;
-                const float k = inv[kBlocksPerThread == 1 ? 0 : g / 2];
-                uint32_t o[4];
+            for (int g2 = 0; g2 < 2; ++g2) {
+                if (half * 64 + g2 * 32 >= c.valid_rows) break;
+                uint32_t o[8];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t w0 = packed[g * 8 + 2 * q], w1 = packed[g * 8 + 2 * q + 1];
+                for (int q = 0; q < 8; ++q) {
+                    const float k = inv[kBlocksPerThread == 1 ? 0 : g2];
+                    const uint32_t w0 = packed[g2 * 16 + 2 * q], w1 = packed[g2 * 16 + 2 * q + 1];
                     o[q] = cvt_e4m3x4(__fmul_rn(bf16_lo(w0), k), __fmul_rn(bf16_hi(w0), k), __fmul_rn(bf16_lo(w1), k),
                                       __fmul_rn(bf16_hi(w1), k));
                 }
-                stg128(dst + g * 16, o[0], o[1], o[2], o[3]);
+                if (wide && half * 64 + g2 * 32 + 16 < c.valid_rows) {
+                    stg256(dst + g2 * 32, o);
+                } else {
+                    stg128(dst + g2 * 32, o[0], o[1], o[2], o[3]);
+                    if (half * 64 + g2 * 32 + 16 < c.valid_rows) stg128(dst + g2 * 32 + 16, o[4], o[5], o[6], o[7]);
+                }
             }
         });
 }
@@ -465,23 +475,29 @@ __global__ void __launch_bounds__(kTileThreads) swiglu_per_channel_cast_kernel(c
                    cvt_e4m3x4(q[8], q[9], q[10], q[11]), cvt_e4m3x4(q[12], q[13], q[14], q[15]));
         }
     } else {
-        // thread = (channel, 64 tokens): 16 consecutive tokens of a channel leave as one 128-bit store
+        // thread = (channel, 64 tokens)
         const int ch = t & 127, half = t >> 7;
         if (ch < valid_cols) {
             uint8_t* dst = p.out + (col0 + ch) * p.num_tokens + row0 + half * 64;
+            const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int r0 = half * 64 + g * 16;
+            for (int g2 = 0; g2 < 2; ++g2) {  // 32 tokens of the channel: one 256-bit store (whole sectors per lane)
+                const int r0 = half * 64 + g2 * 32;
                 const float k = col_inv[r0 / NPT][ch];
-                uint32_t o[4];
+                uint32_t o[8];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < 8; ++q) {
                     float f[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) f[e] = __fmul_rn(__uint_as_float(static_cast<uint32_t>(act[r0 + 4 * q + e][ch]) << 16), k);
                     o[q] = cvt_e4m3x4(f[0], f[1], f[2], f[3]);
                 }
-                stg128(dst + g * 16, o[0], o[1], o[2], o[3]);
+                if (wide) {
+                    stg256(dst + g2 * 32, o);
+                } else {
+                    stg128(dst + g2 * 32, o[0], o[1], o[2], o[3]);
+                    stg128(dst + g2 * 32 + 16, o[4], o[5], o[6], o[7]);
+                }
             }
         }
     }

@@ -520,17 +520,6 @@ int launch_group_kernel(Kernel kernel, TokenCastParams p, int unroll, int sm_lim
     return check_launch(what);
 }
 
-// Steps per work item.  TKQ_GROUP_UNROLL (1, 2 or 4) overrides the default; a tuning aid.
-inline int group_unroll(int dflt, int max_unroll) {
-    static const int forced = [] {
-        const char* e = std::getenv("TKQ_GROUP_UNROLL");
-        return e ? std::atoi(e) : 0;
-    }();
-    int u = forced > 0 ? forced : dflt;
-    if (u > max_unroll) u = max_unroll;
-    return u >= 4 ? 4 : (u >= 2 ? 2 : 1);
-}
-
 // round_sf with a clamp that keeps clamp / MAX a normal number: the division-free scale path applies.
 inline bool can_use_fast_pow2(unsigned flags, float clamp_min, float max_q) {
     return (flags & TKQ_ROUND_SF) && clamp_min >= max_q * 1.1754943508222875e-38f;

@@ -6,7 +6,6 @@ device->host copies run on three streams over a ring of preallocated device stag
 directions and the kernels overlap; per call nothing is allocated.  The kernels are the same ones
 `tilekernels_b200.quant.per_token_cast` launches, called through the C ABI with pointers into the staging ring.
 """
-from typing import Optional
 
 import torch
 
