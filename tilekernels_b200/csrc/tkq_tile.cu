@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "tkq_async.cuh"
 #include "tkq_launch.cuh"
@@ -613,7 +614,7 @@ static int launch_tile(Kernel kernel, TileParams p, int elem_bytes, const char* 
     alignas(64) CUtensorMap tmap;
     if (int rc = make_tensor_map(&tmap, p.x, elem_bytes, p.num_tokens, p.hidden)) return rc;
     const int sms = device_sm_count();
-    const int blocks_per_sm = 2;
+    const int blocks_per_sm = 2;  // three blocks with two stages each measured no faster
     const int grid = static_cast<int>(tiles < static_cast<int64_t>(sms) * blocks_per_sm ? tiles : static_cast<int64_t>(sms) * blocks_per_sm);
     const int max_stages = (100 * 1024) / tile_bytes;  // 3 bf16 tiles or 1 fp32 tile
     const int64_t tiles_per_block = (tiles + grid - 1) / grid;
@@ -668,10 +669,11 @@ struct FusedChannelParams {
 };
 
 template <int IN>
-__global__ void __launch_bounds__(kTileThreads) per_channel_cast_fused_kernel(const FusedChannelParams p) {
-    __shared__ int col_amax_bits[kTile];
-    __shared__ float col_inv[kTile];
-    const int t = threadIdx.x, lane = t & 31;
+__global__ void __launch_bounds__(kTileThreads, 3) per_channel_cast_fused_kernel(const FusedChannelParams p) {
+    __shared__ __align__(16) float warp_max[kTileThreads / 32][kTile];  // column maxima of each warp's 16 rows
+    __shared__ __align__(16) float col_inv[kTile];
+    using Src = typename std::conditional<IN == kInFp8, QuantSource<TKQ_FMT_E4M3>, PlainSource<IN == kInFp8 ? TKQ_DT_BF16 : IN>>::type;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int c16 = t & 7, r_base = t >> 3;
     const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
     const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
@@ -679,59 +681,77 @@ __global__ void __launch_bounds__(kTileThreads) per_channel_cast_fused_kernel(co
     const int valid_cols = static_cast<int>(p.hidden - col0 < kTile ? p.hidden - col0 : kTile);
     const bool col_ok = c16 * 16 < valid_cols;
     const bool round_sf = p.flags & TKQ_ROUND_SF;
-    if (t < kTile) col_amax_bits[t] = 0;
 
-    float v[4][16];
+    // The four chunks stay in registers as loaded (8 words per chunk for bf16, 4 for FP8) and are unpacked twice,
+    // for the maximum and for the conversion: fewer live registers, more resident blocks to hide the two
+    // dependent loads (row index, then row).
+    typename Src::Raw raw[4];
+    float scale_in[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    int64_t src_rows[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int r = r_base + 32 * k;
-        int64_t src_row = -1;
-        if (col_ok && r < valid_rows) src_row = p.pos_to_token != nullptr ? p.pos_to_token[row0 + r] : row0 + r;
-        if (src_row >= 0) {
-            const int64_t elem = src_row * p.hidden + col0 + c16 * 16;
-            if constexpr (IN == kInFp8) {
-                typename QuantSource<TKQ_FMT_E4M3>::Raw raw;
-                QuantSource<TKQ_FMT_E4M3>::issue(raw, static_cast<const uint8_t*>(p.x) + elem, false);
-                QuantSource<TKQ_FMT_E4M3>::unpack(raw, v[k], p.x_sf[src_row * (p.hidden / 128) + (col0 + c16 * 16) / 128]);
-            } else {
-                typename PlainSource<IN>::Raw raw;
-                PlainSource<IN>::issue(raw, static_cast<const uint8_t*>(p.x) + PlainSource<IN>::bytes(elem), p.wide_loads);
-                PlainSource<IN>::unpack(raw, v[k]);
-            }
-        } else {
+        src_rows[k] = -1;
+        if (col_ok && r < valid_rows) src_rows[k] = p.pos_to_token != nullptr ? p.pos_to_token[row0 + r] : row0 + r;
+    }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[k][j] = 0.0f;
+    for (int k = 0; k < 4; ++k) {
+        Src::zero(raw[k]);
+        if (src_rows[k] >= 0) {
+            const int64_t elem = src_rows[k] * p.hidden + col0 + c16 * 16;
+            Src::issue(raw[k], static_cast<const uint8_t*>(p.x) + Src::bytes(elem), p.wide_loads);
+            if constexpr (IN == kInFp8) scale_in[k] = p.x_sf[src_rows[k] * (p.hidden / 128) + (col0 + c16 * 16) / 128];
         }
     }
+    auto unpack = [&](int k, float* v) {
+        if constexpr (IN == kInFp8) Src::unpack(raw[k], v, scale_in[k]);
+        else Src::unpack(raw[k], v);
+    };
     float cm[16];
 #pragma unroll
+    for (int j = 0; j < 16; ++j) cm[j] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; k += 2) {
+        float v0[16], v1[16];
+        unpack(k, v0);
+        unpack(k + 1, v1);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) cm[j] = max3_abs(cm[j], v0[j], v1[j]);
+    }
+#pragma unroll
     for (int j = 0; j < 16; ++j) {
-        cm[j] = max3_abs(fabsf(v[0][j]), v[1][j], max3_abs(0.0f, v[2][j], v[3][j]));
         cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 8));
         cm[j] = fmaxf(cm[j], __shfl_xor_sync(kFullMask, cm[j], 16));
     }
-    __syncthreads();  // col_amax_bits is cleared
     if (lane < 8) {
+        float4* dst = reinterpret_cast<float4*>(&warp_max[warp][c16 * 16]);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) atomicMax(&col_amax_bits[c16 * 16 + j], __float_as_int(cm[j]));
+        for (int q = 0; q < 4; ++q) dst[q] = make_float4(cm[4 * q], cm[4 * q + 1], cm[4 * q + 2], cm[4 * q + 3]);
     }
     __syncthreads();
     if (t < kTile) {
-        const Scale s = make_scale_for<TKQ_FMT_E4M3>(__int_as_float(col_amax_bits[t]), p.clamp_min, round_sf, p.fast_pow2);
+        float m = warp_max[0][t];
+#pragma unroll
+        for (int w = 1; w < kTileThreads / 32; ++w) m = fmaxf(m, warp_max[w][t]);
+        const Scale s = make_scale_for<TKQ_FMT_E4M3>(m, p.clamp_min, round_sf, p.fast_pow2);
         col_inv[t] = s.inv;
         if (t < valid_cols) p.sf[tile_m * p.hidden + col0 + t] = s.sf;
     }
     __syncthreads();
     float inv[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) inv[j] = col_inv[c16 * 16 + j];
+    for (int q = 0; q < 4; ++q) {
+        const float4 a = reinterpret_cast<const float4*>(&col_inv[c16 * 16])[q];
+        inv[4 * q] = a.x, inv[4 * q + 1] = a.y, inv[4 * q + 2] = a.z, inv[4 * q + 3] = a.w;
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int r = r_base + 32 * k;
         if (col_ok && r < valid_rows) {
-            float q[16];
+            float v[16], q[16];
+            unpack(k, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) q[j] = __fmul_rn(v[k][j], inv[j]);
+            for (int j = 0; j < 16; ++j) q[j] = __fmul_rn(v[j], inv[j]);
             stg128(p.out + (row0 + r) * p.hidden + col0 + c16 * 16, cvt_e4m3x4(q[0], q[1], q[2], q[3]),
                    cvt_e4m3x4(q[4], q[5], q[6], q[7]), cvt_e4m3x4(q[8], q[9], q[10], q[11]),
                    cvt_e4m3x4(q[12], q[13], q[14], q[15]));
