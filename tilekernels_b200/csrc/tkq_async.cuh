@@ -19,7 +19,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// Bounded wait: returns false if the phase did not complete within the poll budget (seconds).
+// Bounded wait: returns false if the phase did not complete within the poll limit (seconds).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
     for (int i = 0; i < (1 << 22); ++i) {

@@ -33,6 +33,7 @@ struct ExpandParams {
 };
 
 constexpr int kExpandThreads = 256;
+constexpr int kSfWordsPerLane = 8;  // scale words of a row held in registers: 256 per warp
 
 __device__ __forceinline__ void store32(uint8_t* p, bool wide, const uint32_t* w) {
     if (wide) {
@@ -61,6 +62,14 @@ __global__ void __launch_bounds__(kExpandThreads) expand_to_fused_kernel(const E
         const uint32_t off = step * 1024u + lane * 32u;
         const bool first_half = off < p.row_bytes, second_half = off + 16u < p.row_bytes;
         const int32_t my_pos = lane < p.num_topk ? p.token_topk_to_pos[static_cast<int64_t>(row) * p.num_topk + lane] : -1;
+        // the row's scale words travel with step 0: up to 8 per lane are loaded once, ahead of the stores
+        const bool with_sf = step == 0 && p.x_sf != nullptr;
+        uint32_t sfw[kSfWordsPerLane];
+#pragma unroll
+        for (int j = 0; j < kSfWordsPerLane; ++j) {
+            const uint32_t i = lane + 32u * j;
+            sfw[j] = with_sf && i < p.sf_words ? __ldg(p.x_sf + static_cast<int64_t>(row) * p.sf_words + i) : 0u;
+        }
         uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const uint8_t* src = p.x + static_cast<int64_t>(row) * p.row_bytes + off;
         if (second_half && p.wide) {
@@ -89,9 +98,15 @@ __global__ void __launch_bounds__(kExpandThreads) expand_to_fused_kernel(const E
                 uint8_t* dst = p.out + static_cast<int64_t>(pos) * p.row_bytes + off;
                 if (second_half) store32(dst, p.wide, w);
                 else if (first_half) stg128(dst, w[0], w[1], w[2], w[3]);
-                if (step == 0 && p.x_sf != nullptr)
-                    for (uint32_t i = lane; i < p.sf_words; i += 32)
+                if (with_sf) {
+#pragma unroll
+                    for (int j = 0; j < kSfWordsPerLane; ++j) {
+                        const uint32_t i = lane + 32u * j;
+                        if (i < p.sf_words) *sf_slot(p, pos, i) = sfw[j];
+                    }
+                    for (uint32_t i = lane + 32u * kSfWordsPerLane; i < p.sf_words; i += 32)  // rows of more than 256 scale words
                         *sf_slot(p, pos, i) = __ldg(p.x_sf + static_cast<int64_t>(row) * p.sf_words + i);
+                }
             }
         }
     }

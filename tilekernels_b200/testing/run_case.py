@@ -4,15 +4,16 @@
     python -m tilekernels_b200.testing.run_case --op cfg5 --rows 32768 --launches 3
 
 ops: cfg1 (per-token e4m3, fp32 scales), cfg2_block, cfg2_channel, cfg3 (SwiGLU + cast), cfg4_fp4, cfg4_e5m6,
-cfg5 (per-token e4m3, ue8m0 scales), back_e4m3 / back_e5m6 (dequantisation of cfg4's tensor to bf16).  --rows limits
-the row count (same per-row distribution).
+cfg5 (per-token e4m3, ue8m0 scales), back_e4m3 / back_e5m6 (dequantisation of cfg4's tensor to bf16), bwd (SwiGLU
+backward + cast on cfg3's tensor quantised with power-of-two scales), expand (row expansion of cfg1's FP8 cast with
+ue8m0 scales to 8 positions per token).  --rows limits the row count (same per-row distribution).
 """
 import argparse
 
 import torch
 
-from tilekernels_b200 import quant
-from tilekernels_b200.testing import make_config_input
+from tilekernels_b200 import moe, quant
+from tilekernels_b200.testing import count_bytes, make_config_input
 
 OPS = {
     'cfg1': ('cfg1', lambda x: quant.per_token_cast(x, 'e4m3', 128)),
@@ -23,6 +24,8 @@ OPS = {
     'cfg4_e5m6': ('cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
     'back_e4m3': ('cfg4', lambda q: (quant.cast_back(q, 'bf16', (1, 128)),)),
     'back_e5m6': ('cfg4', lambda q: (quant.cast_back_e5m6(q, 'bf16', (1, q[0].shape[1] // 3 * 2)),)),
+    'bwd': ('cfg3', lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
+    'expand': ('cfg1', lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True)),
     'cfg5': ('cfg5', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, True, True, True)),
 }
 
@@ -39,6 +42,18 @@ def main() -> None:
         x = quant.per_token_cast(x, 'e4m3', 128)
     elif args.op == 'back_e5m6':
         x = quant.per_token_cast(x, 'e5m6', x.shape[1])
+    elif args.op == 'bwd':
+        rows, hidden = x.shape[0], x.shape[1] // 2
+        g = torch.Generator().manual_seed(11)
+        pos = torch.randperm(rows, generator=g).to(torch.int32)
+        token_topk_to_pos = torch.empty(rows, dtype=torch.int32)
+        token_topk_to_pos[pos.long()] = torch.arange(rows, dtype=torch.int32)
+        x = (quant.per_token_cast(x, 'e4m3', 128, round_sf=True), torch.randn((rows, hidden), generator=g).to(torch.bfloat16).cuda(),
+             torch.rand((rows // 8, 8), generator=g).cuda(), pos.cuda(), token_topk_to_pos.view(-1, 8).cuda())
+    elif args.op == 'expand':
+        q, sf = quant.per_token_cast(x, 'e4m3', 128, None, True, True, True)
+        positions = torch.randperm(x.shape[0] * 8, generator=torch.Generator().manual_seed(13)).to(torch.int32)
+        x = ((q, sf.contiguous()), positions.view(-1, 8).cuda(), torch.zeros(x.shape[0] * 8, dtype=torch.int32, device='cuda'))
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for i in range(args.launches):
         if i == args.launches - 1:
@@ -46,9 +61,8 @@ def main() -> None:
         out = op(x)
     stop.record()
     torch.cuda.synchronize()
-    tensors = (list(x) if isinstance(x, tuple) else [x]) + list(out)
-    nbytes = sum(t.numel() * t.element_size() for t in tensors)
-    rows = tensors[0].shape[0]
+    nbytes = count_bytes(x, out)
+    rows = (x[0][0] if isinstance(x[0], tuple) else x[0]).shape[0] if isinstance(x, tuple) else x.shape[0]
     us = start.elapsed_time(stop) * 1e3
     print(f'{args.op}: rows={rows} bytes={nbytes} last launch {us:.1f} us -> {nbytes / us / 1e3:.0f} GB/s (includes host launch overhead)')
 
