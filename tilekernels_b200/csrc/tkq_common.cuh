@@ -325,6 +325,53 @@ __device__ __forceinline__ float swiglu_bf16_in_range(float g, float u) {
 }
 
 // ---------------------------------------------------------------------------
+// Packed fp32 pairs.  sm_100 executes fma / add / mul on two IEEE binary32 values per issued instruction
+// (fma.rn.f32x2 and friends); every element is rounded exactly as by the scalar instruction, so the pair forms
+// below return the same bits as their scalar counterparts above at half the issue slots.  The kernels that are
+// bound by instruction issue (fused SwiGLU casts) use them.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float2 splat2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+
+// tkq_expf_impl<false> on two arguments (no argument clamp: callers guarantee |x| <= 87)
+__device__ __forceinline__ float2 tkq_expf2_noclamp(float2 x) {
+    const float2 t = fma2(x, splat2(1.4426950408889634f), splat2(12582912.0f));
+    const float2 jf = add2(t, splat2(-12582912.0f));
+    float2 r = fma2(jf, splat2(-0.693145751953125f), x);
+    r = fma2(jf, splat2(-1.428606765330187e-06f), r);
+    float2 q = splat2(0.001381455804221332f);
+    q = fma2(q, r, splat2(0.008368736132979393f));
+    q = fma2(q, r, splat2(0.04166838899254799f));
+    q = fma2(q, r, splat2(0.1666652113199234f));
+    q = fma2(q, r, splat2(0.4999999403953552f));
+    const float2 wl = mul2(mul2(r, r), q);
+    const float2 s = add2(splat2(1.0f), r);
+    const float2 e = add2(fma2(s, splat2(-1.0f), splat2(1.0f)), r);  // (1 - s) + r
+    const float2 p = add2(s, add2(e, wl));
+    return make_float2(__uint_as_float(mad_u32(__float_as_uint(t.x), 1u << 23, __float_as_uint(p.x))),
+                       __uint_as_float(mad_u32(__float_as_uint(t.y), 1u << 23, __float_as_uint(p.y))));
+}
+
+// 1 / d refined by one Newton step from the hardware approximation, for both elements
+__device__ __forceinline__ float2 refined_rcp2(float2 d, float2 neg_d) {
+    float2 y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y.x) : "f"(d.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y.y) : "f"(d.y));
+    return fma2(y, fma2(neg_d, y, splat2(1.0f)), y);
+}
+
+// swiglu_bf16_in_range on two (gate, up) pairs
+__device__ __forceinline__ float2 swiglu_bf16_in_range2(float2 g, float2 u) {
+    const float2 d = add2(splat2(1.0f), tkq_expf2_noclamp(mul2(g, splat2(-1.0f))));
+    const float2 neg_d = mul2(d, splat2(-1.0f));
+    const float2 y = refined_rcp2(d, neg_d);
+    const float2 q = mul2(g, y);
+    return mul2(fma2(fma2(neg_d, q, g), y, q), u);
+}
+
+// ---------------------------------------------------------------------------
 // Host-side helpers
 // ---------------------------------------------------------------------------
 int set_error(int code, const char* msg);          // records msg for tkq_last_error_string, returns code

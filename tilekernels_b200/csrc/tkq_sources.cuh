@@ -139,7 +139,11 @@ struct SwigluSource {
         }
         if (bf16_gates && lo >= 9.094947017729282e-13f && hi <= 44.0f) {  // 2^-40 <= |g| <= 44 for the whole chunk
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = swiglu_bf16_in_range(g[i], u[i]);
+            for (int i = 0; i < 16; i += 2) {
+                const float2 y = swiglu_bf16_in_range2(make_float2(g[i], g[i + 1]), make_float2(u[i], u[i + 1]));
+                v[i] = y.x;
+                v[i + 1] = y.y;
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = swiglu(g[i], u[i]);

@@ -44,8 +44,12 @@ struct SwigluBackwardParams {
     bool wide;                 // grad_out, out and x_grad are 32-byte aligned: 256-bit accesses
 };
 
-constexpr int kBackwardThreads = 256;
-constexpr int kBackwardBlocksPerSm = 4;  // 64 registers: measured faster than 2 or 3 blocks with more registers
+constexpr int kBackwardThreads = 128;
+// Resident blocks per SM the register allocation aims at.  With the next step's loads in flight the kernel wants
+// registers more than warps: measured best at 128 registers (4 blocks of 4 warps) without the clamp and at 168
+// (3 blocks) with it; tighter limits spill and were 10-40 % slower.
+template <bool kClamp>
+constexpr int kBackwardBlocksPerSm = kClamp ? 3 : 4;
 
 __device__ __forceinline__ void load_bf16x16(const uint8_t* p, bool wide, uint32_t* w) {
     if (wide) {
@@ -97,57 +101,55 @@ __device__ __forceinline__ float group_max(float m) {
 // the clamp, so exp needs no argument clamp and both quotients come from ONE refined reciprocal (the sequence
 // swiglu_bf16_in_range documents; for the numerator 1 and the 3-bit FP8 mantissas it was compared with IEEE
 // division for all 2^23 denominator mantissas of all 64 binades of [1, 2^64): no difference).
+// Pairs of columns go through the packed fp32 instructions (two IEEE results per issued instruction).
 template <bool kClamp, bool kInRange>
-__device__ __forceinline__ float backward_chunk(const float* g, const float* u, const uint32_t* raw_d, float w, float clamp,
-                                                float acc, float* dg, float* du, uint32_t* o) {
-    float o_even = 0.0f;
+__device__ __forceinline__ float2 backward_chunk(const float* g, const float* u, const uint32_t* raw_d, float w, float clamp,
+                                                 float2 acc, float* dg, float* du, uint32_t* o) {
+    const float2 one = splat2(1.0f), minus_one = splat2(-1.0f), w2 = splat2(w);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        float gi = g[i], ui = u[i];
-        bool clamped_g = false, clamped_u = false;
+    for (int i = 0; i < 16; i += 2) {
+        float2 g2 = make_float2(g[i], g[i + 1]), u2 = make_float2(u[i], u[i + 1]);
+        bool clamped_g0 = false, clamped_g1 = false, clamped_u0 = false, clamped_u1 = false;
         if constexpr (kClamp) {
-            clamped_g = gi > clamp;
-            clamped_u = ui > clamp || ui < -clamp;
-            gi = clamped_g ? clamp : gi;
-            ui = ui > clamp ? clamp : ui;
-            ui = ui < -clamp ? -clamp : ui;
+            clamped_g0 = g2.x > clamp, clamped_g1 = g2.y > clamp;
+            clamped_u0 = u2.x > clamp || u2.x < -clamp, clamped_u1 = u2.y > clamp || u2.y < -clamp;
+            g2.x = clamped_g0 ? clamp : g2.x, g2.y = clamped_g1 ? clamp : g2.y;
+            u2.x = u2.x > clamp ? clamp : u2.x, u2.y = u2.y > clamp ? clamp : u2.y;
+            u2.x = u2.x < -clamp ? -clamp : u2.x, u2.y = u2.y < -clamp ? -clamp : u2.y;
         }
-        const float d = (i & 1) ? bf16_hi(raw_d[i >> 1]) : bf16_lo(raw_d[i >> 1]);
-        float ratio, s;  // g / t and 1 / t, both correctly rounded
+        const float2 d2 = make_float2(bf16_lo(raw_d[i >> 1]), bf16_hi(raw_d[i >> 1]));
+        float2 ratio, s;  // g / t and 1 / t, both correctly rounded
         if constexpr (kInRange) {
-            const float t = __fadd_rn(1.0f, tkq_expf_impl<false>(-gi));
-            float y;
-            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(t));
-            y = __fmaf_rn(y, __fmaf_rn(-t, y, 1.0f), y);
-            s = __fmaf_rn(__fmaf_rn(-t, y, 1.0f), y, y);
-            const float q0 = __fmul_rn(gi, y);
-            ratio = __fmaf_rn(__fmaf_rn(-t, q0, gi), y, q0);
+            const float2 t = add2(one, tkq_expf2_noclamp(mul2(g2, minus_one)));
+            const float2 neg_t = mul2(t, minus_one);
+            const float2 y = refined_rcp2(t, neg_t);
+            s = fma2(fma2(neg_t, y, one), y, y);
+            const float2 q0 = mul2(g2, y);
+            ratio = fma2(fma2(neg_t, q0, g2), y, q0);
         } else {
-            const float t = __fadd_rn(1.0f, tkq_expf(-gi));
-            ratio = __fdiv_rn(gi, t);
-            s = __fdiv_rn(1.0f, t);
+            const float t0 = __fadd_rn(1.0f, tkq_expf(-g2.x)), t1 = __fadd_rn(1.0f, tkq_expf(-g2.y));
+            ratio = make_float2(__fdiv_rn(g2.x, t0), __fdiv_rn(g2.y, t1));
+            s = make_float2(__fdiv_rn(1.0f, t0), __fdiv_rn(1.0f, t1));
         }
-        const float a = __fmul_rn(ratio, ui);
-        acc = __fadd_rn(acc, __fmul_rn(d, a));
-        const float q = __fmul_rn(__fmul_rn(d, w), s);
-        const float oi = __fmul_rn(a, w);
-        if (i & 1) {  // the weighted activation leaves as bf16 pairs
-            const __nv_bfloat162 b = __floats2bfloat162_rn(o_even, oi);
-            o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b);
-        } else {
-            o_even = oi;
-        }
-        const float vg = __fmul_rn(__fmul_rn(q, ui), __fmaf_rn(gi, __fsub_rn(1.0f, s), 1.0f));
-        const float vu = __fmul_rn(q, gi);
-        dg[i] = clamped_g ? 0.0f : vg;
-        du[i] = clamped_u ? 0.0f : vu;
+        const float2 a = mul2(ratio, u2);
+        acc = add2(acc, mul2(d2, a));
+        const float2 q = mul2(mul2(d2, w2), s);
+        const float2 out2 = mul2(a, w2);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(out2.x, out2.y);  // the weighted activation leaves as bf16 pairs
+        o[i >> 1] = *reinterpret_cast<const uint32_t*>(&b);
+        const float2 vg = mul2(mul2(q, u2), fma2(g2, fma2(s, minus_one, one), one));  // q * u * (1 + g * (1 - s))
+        const float2 vu = mul2(q, g2);
+        dg[i] = clamped_g0 ? 0.0f : vg.x;
+        dg[i + 1] = clamped_g1 ? 0.0f : vg.y;
+        du[i] = clamped_u0 ? 0.0f : vu.x;
+        du[i + 1] = clamped_u1 ? 0.0f : vu.y;
     }
     return acc;
 }
 
 // G = 16 * LPG values per scale
 template <int LPG, bool kClamp>
-__global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm) swiglu_backward_kernel(const SwigluBackwardParams p) {
+__global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm<kClamp>) swiglu_backward_kernel(const SwigluBackwardParams p) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t nthreads = gridDim.x * blockDim.x;
@@ -158,54 +160,76 @@ __global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm) swiglu
     for (uint32_t e = tid; e < p.entries; e += nthreads)
         if (p.token_topk_to_pos[e] == -1) p.weight_grad[e] = 0.0f;
 
-    for (uint32_t row = tid >> 5; row < p.rows; row += nthreads >> 5) {
-        const int32_t index = p.pos_to_token_topk[row];
-        const float w = index >= 0 ? p.weight[index] : 0.0f;
-        const uint8_t* x_row = p.x + static_cast<int64_t>(row) * 2 * hidden;
-        const float* sf_row = p.x_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
-        float* out_sf_row = p.x_grad_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
-        float acc = 0.0f;
-        for (uint32_t step = 0; step < p.steps; ++step) {
-            const uint32_t col = step * 512u + lane * 16u;
-            const bool active = col < hidden;  // whole scale groups are active or not: hidden is a multiple of G
-            const uint32_t group = col / (16u * LPG);
-            QuantSource<TKQ_FMT_E4M3>::Raw raw_g, raw_u;
-            QuantSource<TKQ_FMT_E4M3>::zero(raw_g);
-            QuantSource<TKQ_FMT_E4M3>::zero(raw_u);
-            uint32_t raw_d[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            float sf_g = 0.0f, sf_u = 0.0f;
-            if (active) {
-                QuantSource<TKQ_FMT_E4M3>::issue(raw_g, x_row + col, false);
-                QuantSource<TKQ_FMT_E4M3>::issue(raw_u, x_row + hidden + col, false);
-                load_bf16x16(p.grad_out + (static_cast<int64_t>(row) * hidden + col) * 2, p.wide, raw_d);
-                sf_g = __ldg(sf_row + group);
-                sf_u = __ldg(sf_row + groups_per_half + group);
-            }
-            float g[16], u[16];
-            QuantSource<TKQ_FMT_E4M3>::unpack(raw_g, g, sf_g);
-            QuantSource<TKQ_FMT_E4M3>::unpack(raw_u, u, sf_u);
-            float dg[16], du[16];
-            uint32_t o[8];
-            // chunks whose gates are bf16 numbers (an FP8 code times a power-of-two scale) of magnitude in
-            // [2^-40, 44], none clamped, take the cheaper evaluation
-            uint32_t low_bits = 0;
-            float g_min = g[0], g_max = g[0];
+    // A warp walks its rows step by step; the loads of the NEXT step (or of the next row's first step) are issued
+    // before the arithmetic of the current one, so their latency hides behind about 500 instructions.
+    using Q8 = QuantSource<TKQ_FMT_E4M3>;
+    struct StepInput {
+        Q8::Raw g, u;
+        uint32_t d[8];
+        float sf_g, sf_u;
+    };
+    auto load_step = [&](StepInput& in, uint32_t row, uint32_t step) {
+        const uint32_t col = step * 512u + lane * 16u;
+        Q8::zero(in.g);
+        Q8::zero(in.u);
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                low_bits |= __float_as_uint(g[i]) | __float_as_uint(g[i + 1]);
-                g_min = min3_abs(g_min, g[i], g[i + 1]);
-                g_max = max3_abs(g_max, g[i], g[i + 1]);
-            }
-            bool in_range = (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f && g_max <= 44.0f;
-            if constexpr (kClamp) in_range = in_range && g_max <= p.swiglu_clamp;
-            if (in_range) acc = backward_chunk<kClamp, true>(g, u, raw_d, w, p.swiglu_clamp, acc, dg, du, o);
-            else acc = backward_chunk<kClamp, false>(g, u, raw_d, w, p.swiglu_clamp, acc, dg, du, o);
-            const float amax_g = group_max<LPG>(absmax16(dg));
-            const float amax_u = group_max<LPG>(absmax16(du));
-            if (!active) continue;  // after the shuffles: the whole warp takes part in them
+        for (int i = 0; i < 8; ++i) in.d[i] = 0;
+        in.sf_g = in.sf_u = 0.0f;
+        if (row < p.rows && col < hidden) {  // whole scale groups are active or not: hidden is a multiple of G
+            const uint8_t* x_row = p.x + static_cast<int64_t>(row) * 2 * hidden;
+            const float* sf_row = p.x_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
+            const uint32_t group = col / (16u * LPG);
+            Q8::issue(in.g, x_row + col, false);
+            Q8::issue(in.u, x_row + hidden + col, false);
+            load_bf16x16(p.grad_out + (static_cast<int64_t>(row) * hidden + col) * 2, p.wide, in.d);
+            in.sf_g = __ldg(sf_row + group);
+            in.sf_u = __ldg(sf_row + groups_per_half + group);
+        }
+    };
+    auto load_index = [&](uint32_t row) { return row < p.rows ? p.pos_to_token_topk[row] : -1; };
+
+    const uint32_t nwarps = nthreads >> 5;
+    uint32_t row = tid >> 5, step = 0;
+    StepInput cur, next;
+    load_step(cur, row, 0);
+    int32_t index = load_index(row), next_index = -1;
+    float w = index >= 0 ? p.weight[index] : 0.0f;
+    float2 acc2 = make_float2(0.0f, 0.0f);  // dot product of the lane's even and odd columns
+    while (row < p.rows) {
+        const bool last_step = step + 1 == p.steps;
+        const uint32_t next_row = last_step ? row + nwarps : row, next_step = last_step ? 0 : step + 1;
+        load_step(next, next_row, next_step);
+        if (last_step) next_index = load_index(next_row);
+
+        const uint32_t col = step * 512u + lane * 16u;
+        const bool active = col < hidden;
+        const uint32_t group = col / (16u * LPG);
+        float g[16], u[16];
+        Q8::unpack(cur.g, g, cur.sf_g);
+        Q8::unpack(cur.u, u, cur.sf_u);
+        float dg[16], du[16];
+        uint32_t o[8];
+        // chunks whose gates are bf16 numbers (an FP8 code times a power-of-two scale) of magnitude in
+        // [2^-40, 44], none clamped, take the cheaper evaluation
+        uint32_t low_bits = 0;
+        float g_min = g[0], g_max = g[0];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            low_bits |= __float_as_uint(g[i]) | __float_as_uint(g[i + 1]);
+            g_min = min3_abs(g_min, g[i], g[i + 1]);
+            g_max = max3_abs(g_max, g[i], g[i + 1]);
+        }
+        bool in_range = (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f && g_max <= 44.0f;
+        if constexpr (kClamp) in_range = in_range && g_max <= p.swiglu_clamp;
+        if (in_range) acc2 = backward_chunk<kClamp, true>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        else acc2 = backward_chunk<kClamp, false>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        const float amax_g = group_max<LPG>(absmax16(dg));  // the whole warp takes part in the shuffles
+        const float amax_u = group_max<LPG>(absmax16(du));
+        if (active) {
             const Scale scale_g = make_scale_for<TKQ_FMT_E4M3>(amax_g, p.clamp_min, p.round_sf, p.fast_pow2);
             const Scale scale_u = make_scale_for<TKQ_FMT_E4M3>(amax_u, p.clamp_min, p.round_sf, p.fast_pow2);
             if (lane % LPG == 0) {
+                float* out_sf_row = p.x_grad_sf + static_cast<int64_t>(row) * 2 * groups_per_half;
                 out_sf_row[group] = scale_g.sf;
                 out_sf_row[groups_per_half + group] = scale_u.sf;
             }
@@ -217,9 +241,18 @@ __global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm) swiglu
             quantize_store_e4m3x16(dg, scale_g.inv, p.x_grad_fp8 + full_off);
             quantize_store_e4m3x16(du, scale_u.inv, p.x_grad_fp8 + full_off + hidden);
         }
+        if (last_step) {
+            float acc = __fadd_rn(acc2.x, acc2.y);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-        if (lane == 0 && index >= 0) p.weight_grad[index] = acc;
+            for (int o2 = 16; o2 > 0; o2 >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o2));
+            if (lane == 0 && index >= 0) p.weight_grad[index] = acc;
+            acc2 = make_float2(0.0f, 0.0f);
+            index = next_index;
+            w = index >= 0 ? p.weight[index] : 0.0f;
+        }
+        cur = next;
+        row = next_row;
+        step = next_step;
     }
 }
 
