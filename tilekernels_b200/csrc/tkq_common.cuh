@@ -354,6 +354,18 @@ __device__ __forceinline__ float2 tkq_expf2_noclamp(float2 x) {
                        __uint_as_float(mad_u32(__float_as_uint(t.y), 1u << 23, __float_as_uint(p.y))));
 }
 
+// cvt_e5m6_normal for two values, with the scaling folded into the split: for v in the fp16-normal range
+// c = v * (131073 * 2^-112) and d = fma(v, -2^-112, c) are exactly the c and c - vs of the scalar form (scaling
+// by a power of two is exact there), so hi = c - d is the same number.
+__device__ __forceinline__ void cvt_e5m6_normal2(float2 v, uint32_t& c0, uint32_t& c1) {
+    const float2 c = mul2(v, splat2(131073.0f * 1.925929944387236e-34f));
+    const float2 d = fma2(v, splat2(-1.925929944387236e-34f), c);
+    const float2 hi = fma2(d, splat2(-1.0f), c);  // c - d
+    const uint32_t b0 = __float_as_uint(hi.x), b1 = __float_as_uint(hi.y);
+    c0 = mad_u32(b0 >> 31, 0u - 0x3800u, b0 >> 17);
+    c1 = mad_u32(b1 >> 31, 0u - 0x3800u, b1 >> 17);
+}
+
 // 1 / d refined by one Newton step from the hardware approximation, for both elements
 __device__ __forceinline__ float2 refined_rcp2(float2 d, float2 neg_d) {
     float2 y;

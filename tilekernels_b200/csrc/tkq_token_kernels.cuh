@@ -469,12 +469,16 @@ __global__ void __launch_bounds__(kRowMaxThreads) e5m6_row_pipeline_kernel(const
             uint32_t c[16], w[6];
             float smallest = 1.0f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[k][j] = __fmul_rn(v[k][j], sc.inv);
+            for (int j = 0; j < 16; j += 2) {  // packed pairs: one issued instruction scales two values
+                const float2 scaled = mul2(make_float2(v[k][j], v[k][j + 1]), splat2(sc.inv));
+                v[k][j] = scaled.x;
+                v[k][j + 1] = scaled.y;
+            }
 #pragma unroll
             for (int j = 0; j < 16; j += 2) smallest = min3_abs(smallest, v[k][j], v[k][j + 1]);
             if (smallest >= 6.103515625e-05f) {  // every |v| >= 2^-14: the fp16-normal rules apply to the whole chunk
 #pragma unroll
-                for (int j = 0; j < 16; ++j) c[j] = cvt_e5m6_normal(v[k][j]);
+                for (int j = 0; j < 16; j += 2) cvt_e5m6_normal2(make_float2(v[k][j], v[k][j + 1]), c[j], c[j + 1]);
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) c[j] = cvt_e5m6(v[k][j]);
