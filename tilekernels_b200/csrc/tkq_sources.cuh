@@ -179,8 +179,9 @@ struct QuantSource<TKQ_FMT_E4M3> {
                 uint32_t f16x2;
                 asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(f16x2) : "h"(pair));
                 const __half2 hv = *reinterpret_cast<const __half2*>(&f16x2);
-                v[4 * i + 2 * h] = __fmul_rn(__low2float(hv), scale);
-                v[4 * i + 2 * h + 1] = __fmul_rn(__high2float(hv), scale);
+                const float2 t = mul2(__half22float2(hv), splat2(scale));
+                v[4 * i + 2 * h] = t.x;
+                v[4 * i + 2 * h + 1] = t.y;
             }
         }
     }
@@ -204,8 +205,9 @@ struct QuantSource<TKQ_FMT_E2M1> {
             uint32_t f16x2;
             asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(f16x2) : "h"(byte));
             const __half2 hv = *reinterpret_cast<const __half2*>(&f16x2);
-            v[2 * i] = __fmul_rn(__low2float(hv), scale);
-            v[2 * i + 1] = __fmul_rn(__high2float(hv), scale);
+            const float2 t = mul2(__half22float2(hv), splat2(scale));
+            v[2 * i] = t.x;
+            v[2 * i + 1] = t.y;
         }
     }
 };
@@ -224,7 +226,11 @@ __device__ __forceinline__ float absmax16(const float* v) {
 __device__ __forceinline__ void quantize_store_e4m3x16(const float* v, float inv, uint8_t* dst) {
     float s[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], inv);
+    for (int i = 0; i < 16; i += 2) {  // packed pairs: one issued instruction scales two values
+        const float2 t = mul2(make_float2(v[i], v[i + 1]), splat2(inv));
+        s[i] = t.x;
+        s[i + 1] = t.y;
+    }
     stg128(dst, cvt_e4m3x4(s[0], s[1], s[2], s[3]), cvt_e4m3x4(s[4], s[5], s[6], s[7]),
            cvt_e4m3x4(s[8], s[9], s[10], s[11]), cvt_e4m3x4(s[12], s[13], s[14], s[15]));
 }
@@ -233,7 +239,11 @@ __device__ __forceinline__ void quantize_store_e4m3x16(const float* v, float inv
 __device__ __forceinline__ void quantize_store_e2m1x16(const float* v, float inv, uint8_t* dst) {
     float s[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(v[i], inv);
+    for (int i = 0; i < 16; i += 2) {
+        const float2 t = mul2(make_float2(v[i], v[i + 1]), splat2(inv));
+        s[i] = t.x;
+        s[i + 1] = t.y;
+    }
     stg64(dst, cvt_e2m1x8(s), cvt_e2m1x8(s + 8));
 }
 
