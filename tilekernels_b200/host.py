@@ -15,7 +15,7 @@ from .utils import align, ceil_div
 
 
 class HostCastPipeline:
-    def __init__(self, device: torch.device, hidden: int, max_rows: int, chunk_rows: int = 16384, depth: int = 3,
+    def __init__(self, device: torch.device, hidden: int, max_rows: int, chunk_rows: int = 4096, depth: int = 3,
                  in_dtype: torch.dtype = torch.bfloat16):
         assert hidden % 16 == 0 and depth >= 2
         self.device = torch.device(device)
