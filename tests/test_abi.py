@@ -63,3 +63,25 @@ def test_argument_checks_need_no_device(lib):
     assert lib.tkq_per_block_cast(p16, 0, 4, 256, 0, 64, 64, 0, p16, p16, 2, None) == -2
     assert lib.tkq_swiglu_forward_and_per_token_cast(p16, 0, 4, 192, 128, None, None, None, -1.0, None, -1.0, 0, 0, p16, p16, 1,
                                                      None) == -2
+
+
+def test_argument_checks_of_the_backward_and_expand_entry_points(lib):
+    buf = (ctypes.c_char * 4096)()
+    p16 = (ctypes.addressof(buf) + 15) // 16 * 16
+    bwd = lib.tkq_swiglu_backward_and_per_token_cast
+    # (x, x_sf, grad_out, weight, pos_to_token_topk, token_topk_to_pos, rows, hidden, tokens, topk, group, clamp, flags,
+    #  out, x_grad_fp8, x_grad_sf, x_grad, weight_grad, stream)
+    assert bwd(p16, p16, p16, p16, p16, p16, 0, 256, 2, 2, 128, -1.0, 0, p16, p16, p16, p16, p16, None) == 0       # no rows
+    assert bwd(p16, p16, p16, p16, p16, p16, 4, 256, 2, 2, 64, -1.0, 0, p16, p16, p16, p16, p16, None) == -2      # group 64
+    assert bwd(p16, p16, p16, p16, p16, p16, 4, 192, 2, 2, 128, -1.0, 0, p16, p16, p16, p16, p16, None) == -2     # 192 % 128
+    assert bwd(p16, p16, p16, p16, p16, p16, 4, 256, 2, 2, 128, -1.0, 2, p16, p16, p16, p16, p16, None) == -2     # layout flag
+    assert bwd(p16, None, p16, p16, p16, p16, 4, 256, 2, 2, 128, -1.0, 0, p16, p16, p16, p16, p16, None) == -1    # null
+    assert bwd(p16 + 4, p16, p16, p16, p16, p16, 4, 256, 2, 2, 128, -1.0, 0, p16, p16, p16, p16, p16, None) == -3  # alignment
+    expand = lib.tkq_expand_to_fused
+    # (x, tokens, row_bytes, x_sf, sf_words, token_topk_to_pos, topk, pos_to_expert, expanded, flags, out, out_sf, stride, stream)
+    assert expand(p16, 0, 256, None, 0, p16, 2, p16, 8, 0, p16, None, 0, None) == 0                                # no tokens
+    assert expand(p16, 4, 250, None, 0, p16, 2, p16, 8, 0, p16, None, 0, None) == -2                               # 250 % 16
+    assert expand(p16, 4, 256, p16, 0, p16, 2, p16, 8, 0, p16, p16, 2, None) == -1                                 # scales without a count
+    assert expand(p16, 4, 256, None, 0, p16, 2, p16, 8, 4, p16, None, 0, None) == -2                               # unknown flag
+    assert expand(p16 + 8, 4, 256, None, 0, p16, 2, p16, 8, 0, p16, None, 0, None) == -3                           # alignment
+    assert b'expand_to_fused' in lib.tkq_last_error_string()

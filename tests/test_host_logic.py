@@ -90,3 +90,25 @@ def test_entry_points_assert_before_any_launch():
                  lambda: quant.per_token_cast(x, 'e5m6', 256)):
         with pytest.raises(AssertionError):
             call()
+
+
+def test_neighbour_entry_points_assert_before_any_launch():
+    from tilekernels_b200 import moe, quant
+    q = torch.zeros((8, 512), dtype=torch.float8_e4m3fn)
+    sf = torch.ones((8, 4), dtype=torch.float32)
+    grad = torch.zeros((8, 256), dtype=torch.bfloat16)
+    weight = torch.ones((4, 2), dtype=torch.float32)
+    pos = torch.arange(8, dtype=torch.int32)
+    t2p = torch.arange(8, dtype=torch.int32).view(4, 2)
+    calls = (
+        lambda: quant.swiglu_backward_and_per_token_cast((q, sf), grad, weight, pos, t2p, 128),       # CPU tensors
+        lambda: quant.swiglu_backward_and_per_token_cast((q, sf), grad, weight, pos, t2p, 64),        # group size
+        lambda: quant.cast_back((q, sf), 'bf16', (1, 128)),
+        lambda: quant.per_channel_cast_and_transpose(grad, 'e4m3', 128),
+        lambda: moe.expand_to_fused(grad, t2p, pos),
+        lambda: moe.expand_to_fused_with_sf((q, sf), 64, t2p, pos),                                   # group size
+        lambda: moe.expand_to_fused_with_sf((q, sf.to(torch.int32)), 128, t2p, pos, False),          # packed needs column-major
+    )
+    for call in calls:
+        with pytest.raises(AssertionError):
+            call()
