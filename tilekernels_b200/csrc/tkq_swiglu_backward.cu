@@ -97,12 +97,20 @@ __device__ __forceinline__ float group_max(float m) {
     return m;
 }
 
-// The arithmetic of one lane's 16 columns.  kInRange: every gate is a bf16 number of magnitude in [2^-40, 44] below
-// the clamp, so exp needs no argument clamp and both quotients come from ONE refined reciprocal (the sequence
-// swiglu_bf16_in_range documents; for the numerator 1 and the 3-bit FP8 mantissas it was compared with IEEE
-// division for all 2^23 denominator mantissas of all 64 binades of [1, 2^64): no difference).
+// The arithmetic of one lane's 16 columns, in one of three forms that give the same bits:
+//   kPathBf16InRange  every gate is a bf16 number (an FP8 code times a power-of-two scale) of magnitude in
+//                     [2^-40, 44] below the clamp: exp needs no argument clamp and both quotients come from ONE
+//                     refined reciprocal (the sequence swiglu_bf16_in_range documents; for the numerator 1 and the
+//                     3-bit FP8 mantissas it was compared with IEEE division for all 2^23 denominator mantissas of
+//                     all 64 binades of [1, 2^64): no difference);
+//   kPathInRange      gates of any mantissa with |g| <= 44 (FP8 codes times arbitrary fp32 scales): the same exp and
+//                     the same reciprocal for s = 1 / t (its numerator is 1 whatever the gate is), IEEE division
+//                     for g / t;
+//   kPathGeneral      everything else: clamped exp argument, two IEEE divisions.
+constexpr int kPathGeneral = 0, kPathBf16InRange = 1, kPathInRange = 2;
+
 // Pairs of columns go through the packed fp32 instructions (two IEEE results per issued instruction).
-template <bool kClamp, bool kInRange>
+template <bool kClamp, int kPath>
 __device__ __forceinline__ float2 backward_chunk(const float* g, const float* u, const uint32_t* raw_d, float w, float clamp,
                                                  float2 acc, float* dg, float* du, uint32_t* o) {
     const float2 one = splat2(1.0f), minus_one = splat2(-1.0f), w2 = splat2(w);
@@ -119,13 +127,19 @@ __device__ __forceinline__ float2 backward_chunk(const float* g, const float* u,
         }
         const float2 d2 = make_float2(bf16_lo(raw_d[i >> 1]), bf16_hi(raw_d[i >> 1]));
         float2 ratio, s;  // g / t and 1 / t, both correctly rounded
-        if constexpr (kInRange) {
+        if constexpr (kPath == kPathBf16InRange) {
             const float2 t = add2(one, tkq_expf2_noclamp(mul2(g2, minus_one)));
             const float2 neg_t = mul2(t, minus_one);
             const float2 y = refined_rcp2(t, neg_t);
             s = fma2(fma2(neg_t, y, one), y, y);
             const float2 q0 = mul2(g2, y);
             ratio = fma2(fma2(neg_t, q0, g2), y, q0);
+        } else if constexpr (kPath == kPathInRange) {
+            const float2 t = add2(one, tkq_expf2_noclamp(mul2(g2, minus_one)));
+            const float2 neg_t = mul2(t, minus_one);
+            const float2 y = refined_rcp2(t, neg_t);
+            s = fma2(fma2(neg_t, y, one), y, y);
+            ratio = make_float2(__fdiv_rn(g2.x, t.x), __fdiv_rn(g2.y, t.y));
         } else {
             const float t0 = __fadd_rn(1.0f, tkq_expf(-g2.x)), t1 = __fadd_rn(1.0f, tkq_expf(-g2.y));
             ratio = make_float2(__fdiv_rn(g2.x, t0), __fdiv_rn(g2.y, t1));
@@ -209,8 +223,7 @@ __global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm<kClamp>
         Q8::unpack(cur.u, u, cur.sf_u);
         float dg[16], du[16];
         uint32_t o[8];
-        // chunks whose gates are bf16 numbers (an FP8 code times a power-of-two scale) of magnitude in
-        // [2^-40, 44], none clamped, take the cheaper evaluation
+        // pick the cheapest evaluation the chunk's gates allow (see backward_chunk)
         uint32_t low_bits = 0;
         float g_min = g[0], g_max = g[0];
 #pragma unroll
@@ -219,10 +232,12 @@ __global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm<kClamp>
             g_min = min3_abs(g_min, g[i], g[i + 1]);
             g_max = max3_abs(g_max, g[i], g[i + 1]);
         }
-        bool in_range = (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f && g_max <= 44.0f;
+        bool in_range = g_max <= 44.0f;
         if constexpr (kClamp) in_range = in_range && g_max <= p.swiglu_clamp;
-        if (in_range) acc2 = backward_chunk<kClamp, true>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
-        else acc2 = backward_chunk<kClamp, false>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        const bool bf16_in_range = in_range && (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f;
+        if (bf16_in_range) acc2 = backward_chunk<kClamp, kPathBf16InRange>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        else if (in_range) acc2 = backward_chunk<kClamp, kPathInRange>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        else acc2 = backward_chunk<kClamp, kPathGeneral>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
         const float amax_g = group_max<LPG>(absmax16(dg));  // the whole warp takes part in the shuffles
         const float amax_u = group_max<LPG>(absmax16(du));
         if (active) {
