@@ -144,6 +144,15 @@ struct SwigluSource {
                 v[i] = y.x;
                 v[i + 1] = y.y;
             }
+        } else if (hi <= 44.0f) {  // gates of any mantissa (fp32 input): exp without its clamp, IEEE division
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+                const float2 g2 = make_float2(g[i], g[i + 1]);
+                const float2 d = add2(splat2(1.0f), tkq_expf2_noclamp(mul2(g2, splat2(-1.0f))));
+                const float2 y = mul2(make_float2(__fdiv_rn(g2.x, d.x), __fdiv_rn(g2.y, d.y)), make_float2(u[i], u[i + 1]));
+                v[i] = y.x;
+                v[i + 1] = y.y;
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = swiglu(g[i], u[i]);
