@@ -118,24 +118,37 @@ struct SwigluSource {
         float g[16], u[16];
         P::unpack(r.g, g);
         P::unpack(r.u, u);
-        if (kClamp) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                if (kCount) {
-                    cnt.gate_hi += g[i] > clamp;
-                    cnt.up_hi += u[i] > clamp;
-                    cnt.up_lo += u[i] < -clamp;
-                }
-                g[i] = g[i] > clamp ? clamp : g[i];
-                u[i] = u[i] > clamp ? clamp : u[i];
-                u[i] = u[i] < -clamp ? -clamp : u[i];
-            }
-        }
-        float lo = 1.0f, hi = 0.0f;
+        float lo = 1.0f, hi = 0.0f;  // smallest and largest gate magnitude of the chunk
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
             lo = min3_abs(lo, g[i], g[i + 1]);
             hi = max3_abs(hi, g[i], g[i + 1]);
+        }
+        if (kClamp) {
+            // the clamp (and its counters) only when something in the chunk can reach it: one maximum per two values
+            // instead of three comparisons and three selects per value
+            float u_hi = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) u_hi = max3_abs(u_hi, u[i], u[i + 1]);
+            if (hi > clamp || u_hi > clamp) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (kCount) {
+                        cnt.gate_hi += g[i] > clamp;
+                        cnt.up_hi += u[i] > clamp;
+                        cnt.up_lo += u[i] < -clamp;
+                    }
+                    g[i] = g[i] > clamp ? clamp : g[i];
+                    u[i] = u[i] > clamp ? clamp : u[i];
+                    u[i] = u[i] < -clamp ? -clamp : u[i];
+                }
+                lo = 1.0f, hi = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    lo = min3_abs(lo, g[i], g[i + 1]);
+                    hi = max3_abs(hi, g[i], g[i + 1]);
+                }
+            }
         }
         if (bf16_gates && lo >= 9.094947017729282e-13f && hi <= 44.0f) {  // 2^-40 <= |g| <= 44 for the whole chunk
 #pragma unroll

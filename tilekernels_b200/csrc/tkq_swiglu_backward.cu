@@ -232,12 +232,26 @@ __global__ void __launch_bounds__(kBackwardThreads, kBackwardBlocksPerSm<kClamp>
             g_min = min3_abs(g_min, g[i], g[i + 1]);
             g_max = max3_abs(g_max, g[i], g[i + 1]);
         }
-        bool in_range = g_max <= 44.0f;
-        if constexpr (kClamp) in_range = in_range && g_max <= p.swiglu_clamp;
+        const bool in_range = g_max <= 44.0f;
         const bool bf16_in_range = in_range && (low_bits & 0xFFFFu) == 0 && g_min >= 0x1p-40f;
-        if (bf16_in_range) acc2 = backward_chunk<kClamp, kPathBf16InRange>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
-        else if (in_range) acc2 = backward_chunk<kClamp, kPathInRange>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
-        else acc2 = backward_chunk<kClamp, kPathGeneral>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        bool reaches_clamp = false;  // chunks that cannot reach the clamp take the code without it
+        if constexpr (kClamp) {
+            float u_max = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) u_max = max3_abs(u_max, u[i], u[i + 1]);
+            reaches_clamp = g_max > p.swiglu_clamp || u_max > p.swiglu_clamp;
+        }
+        if (reaches_clamp) {
+            // clamped gates are at most the clamp value, which need not be a bf16 number: general mantissas
+            if (in_range && p.swiglu_clamp <= 44.0f) acc2 = backward_chunk<true, kPathInRange>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+            else acc2 = backward_chunk<true, kPathGeneral>(g, u, cur.d, w, p.swiglu_clamp, acc2, dg, du, o);
+        } else if (bf16_in_range) {
+            acc2 = backward_chunk<false, kPathBf16InRange>(g, u, cur.d, w, 0.0f, acc2, dg, du, o);
+        } else if (in_range) {
+            acc2 = backward_chunk<false, kPathInRange>(g, u, cur.d, w, 0.0f, acc2, dg, du, o);
+        } else {
+            acc2 = backward_chunk<false, kPathGeneral>(g, u, cur.d, w, 0.0f, acc2, dg, du, o);
+        }
         const float amax_g = group_max<LPG>(absmax16(dg));  // the whole warp takes part in the shuffles
         const float amax_u = group_max<LPG>(absmax16(du));
         if (active) {
