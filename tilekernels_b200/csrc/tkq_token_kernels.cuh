@@ -438,6 +438,7 @@ __global__ void __launch_bounds__(kRowMaxThreads) e5m6_row_pipeline_kernel(const
         uint8_t* stage = ring + static_cast<size_t>(s) * stage_bytes;
         if (!mbar_wait(full_bar + s, static_cast<uint32_t>(i / stages) & 1u)) {
             atomicExch(&g_row_wait_failed, 1u);
+            if (t == 0) bulk_store_wait_all();  // rows already handed to the store engine still read this block's ring
             return;
         }
         // the thread's K chunks of 16 values
