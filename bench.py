@@ -240,6 +240,18 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
     return results
 
 
+def cpu_model() -> str:
+    """Model name of the host CPU (first entry of /proc/cpuinfo), for the CPU baseline's record."""
+    try:
+        with open('/proc/cpuinfo') as f:
+            for line in f:
+                if line.lower().startswith('model name'):
+                    return line.split(':', 1)[1].strip()
+    except OSError:
+        pass
+    return 'unknown'
+
+
 def oracle_rate(rows: int, threads: int, repeats: int = 1) -> float:
     """Mtokens/s of the CPU oracle on `rows` rows of the cfg5 workload (best of `repeats`)."""
     import torch
@@ -287,7 +299,7 @@ def run_reference(args) -> None:
         'config': {'workload': f'cfg5 per-token FP8 e4m3 cast, group 128, ue8m0 col-major scales, bf16 [{TOTAL_ROWS},{HIDDEN}]',
                    'sample': sample},
         'hbm_gbs': round(value * bytes_per_token() / 1e3, 3),
-        'cpu_baseline': {'value': round(value, 3), 'unit': 'Mtokens/s', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'cpu_baseline': {'value': round(value, 3), 'unit': 'Mtokens/s', 'cores': cores, 'kind': 'port', 'sample': sample, 'cpu': cpu_model()},
         'e2e': {'value': round(value, 3), 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
@@ -380,7 +392,7 @@ def run_ours(args) -> None:
             cores = os.cpu_count() or 1
             sample_rows = 32768
             line['cpu_baseline'] = {'value': round(oracle_rate(sample_rows, cores, repeats=3), 3), 'unit': 'Mtokens/s', 'cores': cores,
-                                    'kind': 'port', 'sample': f'{sample_rows} of {TOTAL_ROWS} rows, best of 3'}
+                                    'kind': 'port', 'sample': f'{sample_rows} of {TOTAL_ROWS} rows, best of 3', 'cpu': cpu_model()}
             if not args.no_ops:
                 del x
                 torch.cuda.empty_cache()
