@@ -78,11 +78,10 @@ static int dispatch_e5m6(const TokenCastParams& p, cudaStream_t stream) {
     constexpr int EB = DT == TKQ_DT_BF16 ? 2 : 4;
     const uint32_t stage_bytes = static_cast<uint32_t>((p.hidden * EB + 127) / 128 * 128);
     if (p.hidden % 32 == 0 && stage_bytes <= 96 * 1024) {
-        // blocks of about 256 threads so that several blocks (and their rings) share an SM
-#ifndef TKQ_E5_THREADS
-#define TKQ_E5_THREADS 256
-#endif
-        if (row_shape(p.hidden / 16, TKQ_E5_THREADS, &k, &threads)) {
+        // small blocks (up to 128 threads, up to four chunks per thread) so that many blocks and their rings share an
+        // SM: 134 us against 146 us with 256-thread blocks on [32768, 7168]
+        if (row_shape(p.hidden / 16, 128, &k, &threads) || row_shape(p.hidden / 16, 256, &k, &threads) ||
+            row_shape(p.hidden / 16, 512, &k, &threads)) {
             const uint32_t stages = stage_bytes <= 16 * 1024 ? 3u : 2u;
             switch (k) {
                 case 1: return launch_e5m6_pipeline<DT, 1>(p, threads, stages, stage_bytes, stream);
