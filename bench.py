@@ -379,8 +379,9 @@ def run_ours(args) -> None:
             'hbm_gbs': round(kernel_gbs * world, 1),
             'pct_of_8tbs': round(kernel_gbs / 8000.0 * 100, 1),
             'clocks': clocks,
-            'e2e': {'value': round(e2e_value, 3), 'unit': 'Mtokens/s', 'h2d_bytes_per_step': rows * HIDDEN * 2,
-                    'd2h_bytes_per_step': rows * HIDDEN + rows * (HIDDEN // GROUP), 'steps': e2e_steps,
+            # bytes of all ranks together, like `value`
+            'e2e': {'value': round(e2e_value, 3), 'unit': 'Mtokens/s', 'h2d_bytes_per_step': total_rows * HIDDEN * 2,
+                    'd2h_bytes_per_step': total_rows * HIDDEN + total_rows * (HIDDEN // GROUP), 'steps': e2e_steps,
                     'api': 'tilekernels_b200.host.HostCastPipeline.per_token_cast_host (pinned host buffers)'},
             'gpu_launches': args.steps,
             'roofline': {'bound': 'hbm', 'achieved': round(kernel_gbs, 1), 'peak': peak, 'unit': 'GB/s',
