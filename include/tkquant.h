@@ -48,6 +48,7 @@ extern "C" {
 #define TKQ_SF_UE8M0 4u     /* exponent bytes, four per 32-bit word; needs TKQ_SF_COL_MAJOR */
 #define TKQ_SF_ONLY 8u      /* compute and store scales only; `out` is not touched */
 #define TKQ_CAST_ONLY 16u   /* read row-major fp32 scales from `sf`, store data only */
+#define TKQ_EXACT_CODES 32u /* fused SwiGLU cast only: evaluate every activation with the exact routine (see there) */
 
 /* negative return codes */
 #define TKQ_E_BAD_ARG (-1)     /* null pointer, negative size, unknown enum */
@@ -61,13 +62,30 @@ int tkq_version(void);
 const char* tkq_last_error_string(void);
 
 /*
- * Device-side failure flag.  The tile kernels (per-block, per-channel) wait for their
- * shared-memory tile with a bounded number of polls; a kernel that runs out of polls
- * raises a flag and returns without writing.  This call synchronises the device,
- * returns 1 if the flag was raised since the last call (and clears it), 0 if not,
- * -1 if the flag could not be read.  No counterpart in the reference.
+ * Device-side conditions, reported without trapping.  This call synchronises the current device, returns the OR of
+ * the bits below for what was raised on it since the last call (and clears them), 0 if nothing was, -1 if the
+ * flags could not be read.  No counterpart in the reference.
+ *
+ *   TKQ_DEVICE_WAIT_TIMEOUT   a kernel that waits for asynchronous copies into shared memory (the per-block and
+ *                             per-channel tile kernels, the E5M6 row pipeline, the staged SwiGLU cast) ran out of
+ *                             polls (a limit that is seconds long), and returned early.  Outputs of that launch
+ *                             are undefined: rows or tiles may be missing or partly written.
+ *   TKQ_DEVICE_LOSSLESS_RANGE tkq_per_block_cast_lossless met an input scale more than 2^5 below its output
+ *                             block's scale, where the reference's kernel asserts
+ *                             (tile_kernels/quant/per_block_cast_lossless_kernel.py:128); those values were rounded
+ *                             to nearest instead of being represented exactly.
  */
+#define TKQ_DEVICE_WAIT_TIMEOUT 1
+#define TKQ_DEVICE_LOSSLESS_RANGE 2
 int tkq_device_error(void);
+
+/*
+ * Self-test of the bounded wait: launches one warp that receives 16 bytes from `src16` by bulk copy, writes the
+ * first word to `echo` (optional), then waits `poll_limit` polls (1..65536) on a barrier nothing ever arrives on,
+ * gives up, raises TKQ_DEVICE_WAIT_TIMEOUT and returns.  No copy is in flight when it returns and nothing faults
+ * or hangs; tkq_device_error() afterwards reads 1, then 0.  No counterpart in the reference.
+ */
+int tkq_selftest_bounded_wait(const void* src16, unsigned poll_limit, void* echo, void* stream);
 
 /*
  * Per-token cast to FP8 e4m3 or FP4 e2m1: one scale per (1 x num_per_channels) group.
@@ -182,7 +200,7 @@ int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t num_tokens, i
  * (largest input exponent inside it) - 6, not below 0; value = fp4 * 2^(e_in - e_out).
  * Replaces the launch in tile_kernels/quant/per_block_cast_lossless_kernel.py:201-202 (kernel :76-150).  The
  * reference asserts e_in + 5 >= e_out on the device (exact representability); this library rounds to nearest
- * where that does not hold.
+ * where that does not hold and raises TKQ_DEVICE_LOSSLESS_RANGE (see tkq_device_error).
  *
  *   x          [num_tokens, hidden / 2] bytes, x_row_stride in VALUES; x_sf as in tkq_per_token_cast_quantized
  *   out blocks (1 | 32 | 128) x (32 | 128), multiples of the input block; hidden % 32 == 0

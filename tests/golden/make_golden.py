@@ -168,6 +168,46 @@ def gen_swiglu() -> None:
     np.savez_compressed(os.path.join(HERE, 'swiglu.npz'), **store)
 
 
+def gen_swiglu_cfg3() -> None:
+    """The fused SwiGLU cast on the benchmark workload itself (cfg3, [16384, 4096] bf16 ~ N(0,1), gate | up halves
+    of 2048) at reduced row counts: cast(swiglu_forward(x), 'e4m3', (1, 128)) from the reference (the sequence of
+    tests/quant/test_swiglu_forward_and_per_token_cast.py:91-110, formula tile_kernels/torch/swiglu.py:61-75).
+    Large enough for the tolerance on the codes (at most one code apart on at most 1e-4 of the elements) to mean
+    something: 1024 rows = 2.1 M activations = 16384 scale groups for the default flags; 512 rows for the
+    power-of-two scales in the packed-ue8m0 layout; 256 rows for the variant with row weights, clamp and clamp
+    counters.  The
+    inputs are not stored: make_config_input('cfg3', rows) regenerates them and their digest is checked."""
+    store = {}
+    x = make_config_input('cfg3', 1024)
+    store['x1024.sha256'] = np.array(sha(x))
+    out, sf = cast(swiglu_forward(x), 'e4m3', (1, 128))
+    put(store, 'plain/000/out', out)
+    put(store, 'plain/000/sf', sf)
+    x = x[:512]
+    y = swiglu_forward(x)
+    out, sf = cast(y, 'e4m3', (1, 128), round_sf=True, use_tma_aligned_col_major_sf=True, use_packed_ue8m0=True)
+    put(store, 'plain/111/out', out)
+    put(store, 'plain/111/sf', sf)
+    # row weights (a permutation of (token, k) pairs with holes), clamp 2.5 (about 0.6 % of the gates, 1.2 % of the
+    # up values) and the three clamp counters
+    x = x[:256]
+    g = torch.Generator().manual_seed(31)
+    pos = torch.randperm(256, generator=g).to(torch.int32)
+    pos[::13] = -1
+    w = torch.rand((32, 8), generator=g)
+    put(store, 'moe/pos_to_token_topk', pos)
+    put(store, 'moe/topk_weights', w)
+    counts = torch.zeros(3, dtype=torch.int64)
+    y = swiglu_forward(x, pos, w, 2.5, counts)
+    put(store, 'moe/counts', counts)
+    for col, rnd, ue in ((False, False, False), (True, True, True)):
+        out, sf = cast(y, 'e4m3', (1, 128), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+        key = f'moe/{int(col)}{int(rnd)}{int(ue)}'
+        put(store, key + '/out', out)
+        put(store, key + '/sf', sf)
+    np.savez_compressed(os.path.join(HERE, 'swiglu_cfg3.npz'), **store)
+
+
 def gen_requant() -> None:
     """Already quantized inputs (FP8 / FP4 data + scales in every layout) cast again per token, and the fused
     per-channel cast with FP8 input and row gather (reference: tile_kernels/torch/cast.py:86-97,
@@ -350,7 +390,7 @@ def gen_config_digests() -> None:
 
 if __name__ == '__main__':
     torch.set_num_threads(8)
-    generators = {'cast': gen_cast, 'e5m6': gen_e5m6, 'e2m1_kat': gen_e2m1_kat, 'swiglu': gen_swiglu, 'requant': gen_requant,
+    generators = {'cast': gen_cast, 'e5m6': gen_e5m6, 'e2m1_kat': gen_e2m1_kat, 'swiglu': gen_swiglu, 'swiglu_cfg3': gen_swiglu_cfg3, 'requant': gen_requant,
                   'cast_back': gen_cast_back, 'swiglu_backward': gen_swiglu_backward, 'expand': gen_expand, 'config_digests': gen_config_digests}
     for name in (sys.argv[1:] or list(generators)):   # optional arguments: the fixtures to (re)generate
         generators[name]()

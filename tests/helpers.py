@@ -47,3 +47,26 @@ def to_host(t: torch.Tensor) -> torch.Tensor:
 
 def flags_id(flags) -> str:
     return ''.join(str(int(f)) for f in flags)
+
+
+def swiglu_cast_differences(out: torch.Tensor, sf: torch.Tensor, out_ref: torch.Tensor, sf_ref: torch.Tensor, group: int,
+                            sf_to_float) -> dict:
+    """Counts behind the acceptance rule of the fused SwiGLU cast: scales identical, FP8 codes at most one code
+    apart on at most 1e-4 of the elements, dequantised values of equal codes within 1e-3 (relative).
+
+    All four tensors on the CPU, scales in the same layout; `sf_to_float` turns either scale format into fp32."""
+    assert out.shape == out_ref.shape and sf.shape == sf_ref.shape and sf.dtype == sf_ref.dtype
+    s, s_ref = sf_to_float(sf), sf_to_float(sf_ref)
+    ulp = (s.contiguous().view(torch.int32) - s_ref.contiguous().view(torch.int32)).abs()
+    a, b = out.contiguous().view(torch.uint8).to(torch.int32), out_ref.contiguous().view(torch.uint8).to(torch.int32)
+    diff = (a - b).abs()
+    hidden = out.shape[1]
+    dq = out.float() * s.repeat_interleave(group, dim=1)[:, :hidden]
+    dq_ref = out_ref.float() * s_ref.repeat_interleave(group, dim=1)[:, :hidden]
+    same = diff == 0
+    rel = ((dq - dq_ref).abs() / dq_ref.abs().clamp_min(1e-30))[same]
+    return {
+        'scales': ulp.numel(), 'scales_differing': int((ulp > 0).sum()), 'scale_max_ulp': int(ulp.max()) if ulp.numel() else 0,
+        'codes': diff.numel(), 'codes_differing': int((diff > 0).sum()), 'code_max_step': int(diff.max()) if diff.numel() else 0,
+        'dequant_max_rel_equal_codes': float(rel.max()) if rel.numel() else 0.0,
+    }

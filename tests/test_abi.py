@@ -85,3 +85,31 @@ def test_argument_checks_of_the_backward_and_expand_entry_points(lib):
     assert expand(p16, 4, 256, None, 0, p16, 2, p16, 8, 4, p16, None, 0, None) == -2                               # unknown flag
     assert expand(p16 + 8, 4, 256, None, 0, p16, 2, p16, 8, 0, p16, None, 0, None) == -3                           # alignment
     assert b'expand_to_fused' in lib.tkq_last_error_string()
+
+
+@pytest.mark.gpu
+def test_bounded_wait_gives_up_and_reports(oracle, cuda_device):
+    """The waits on asynchronous copies are bounded.  The self-test kernel receives one real copy, then waits a few
+    thousand polls on a barrier nothing arrives on: it must return (nothing in flight, nothing faults), the device
+    condition must read TKQ_DEVICE_WAIT_TIMEOUT once and then clear, and the next ordinary cast must be exact."""
+    import torch
+    from helpers import to_host
+    from tilekernels_b200 import _lib, quant
+    from tilekernels_b200.testing import assert_equal
+    lib = _lib.lib()
+    assert lib.tkq_device_error() == 0
+    src = torch.arange(4, dtype=torch.int32, device=cuda_device) + 1234
+    echo = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    assert lib.tkq_selftest_bounded_wait(src.data_ptr(), 4096, echo.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(echo.item()) == 1234          # the real copy arrived before the wait that runs out
+    assert lib.tkq_device_error() == 1       # TKQ_DEVICE_WAIT_TIMEOUT
+    assert lib.tkq_device_error() == 0
+    assert lib.tkq_selftest_bounded_wait(src.data_ptr(), 0, None, stream) == -1   # limit out of range: nothing launched
+    x = torch.randn((256, 512), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    out, sf = quant.per_block_cast(x.to(cuda_device), 'e4m3', (128, 128))
+    want = oracle.cast(x, 'e4m3', (128, 128))
+    assert_equal(to_host(out), want[0])
+    assert_equal(to_host(sf), want[1])
+    assert lib.tkq_device_error() == 0

@@ -103,3 +103,22 @@ def test_per_block_cast_lossless(oracle, cuda_device, num_tokens, hidden, out_bl
     back_in = oracle.cast_back((q_ref, qsf_ref), 'fp32', (1, 32))
     back_out = oracle.cast_back((to_host(out), to_host(sf)), 'fp32', out_block)
     assert_equal(back_out, back_in)
+
+
+def test_per_block_cast_lossless_reports_range_violation(cuda_device):
+    """Where the reference's kernel asserts on the device (an input scale more than 2^5 below its output block's
+    scale, tile_kernels/quant/per_block_cast_lossless_kernel.py:128), this library finishes the cast and raises
+    TKQ_DEVICE_LOSSLESS_RANGE (2), once, through tkq_device_error()."""
+    from tilekernels_b200 import _lib, quant
+    lib = _lib.lib()
+    assert lib.tkq_device_error() == 0
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((256, 256), generator=g)
+    q, qsf = quant.per_token_cast(x.to(cuda_device), 'e2m1', 32, None, False, True, False)
+    quant.per_block_cast_lossless((q, qsf), 'e4m3', (1, 32), (128, 128), False, True, False)
+    assert lib.tkq_device_error() == 0              # ordinary data: every block within range
+    x[:, 32:64] *= 2.0 ** -12                        # one 32-wide input block 2^12 below its neighbours
+    q, qsf = quant.per_token_cast(x.to(cuda_device), 'e2m1', 32, None, False, True, False)
+    quant.per_block_cast_lossless((q, qsf), 'e4m3', (1, 32), (128, 128), False, True, False)
+    assert lib.tkq_device_error() == 2
+    assert lib.tkq_device_error() == 0

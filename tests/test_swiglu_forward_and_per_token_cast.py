@@ -1,7 +1,13 @@
-"""swiglu_forward_and_per_token_cast on the GPU against the oracle, bit for bit (the oracle and the kernel
-share one exp routine).  Parametrised after the reference's
+"""swiglu_forward_and_per_token_cast on the GPU against the oracle.  Parametrised after the reference's
 tests/quant/test_swiglu_forward_and_per_token_cast.py:34-133: weights on/off, pos_to_expert masking on/off,
-group 128 or hidden, clamp None / 10 / 0.5 with exact clamp counters, two SM counts."""
+group 128 or hidden, clamp None / 10 / 0.5 with exact clamp counters, two SM counts.
+
+Scales and clamp counters equal the oracle's bit for bit in every case.  The FP8 codes equal the oracle's bit
+for bit when the exact evaluation is selected (config.set_exact_swiglu_codes) and wherever the library has no
+approximate kernel (fp32 input, one scale per token, rows shorter than 1024); by default the bf16 / group-128
+kernel derives them from hardware-approximate exp and reciprocal, and the rule is: at most one code apart, on at
+most 1e-4 of the elements.  One element of a small tensor is already more than 1e-4 of it, so a case of fewer
+than 10^6 elements may hold ONE such element and the rate is asserted over all cases together at the end."""
 import pytest
 import torch
 
@@ -9,6 +15,22 @@ from helpers import flags_id, to_host
 from tilekernels_b200.testing import assert_equal
 
 pytestmark = pytest.mark.gpu
+
+_totals = {'codes': 0, 'differing': 0, 'cases': 0}
+
+
+def _check_codes(out_h: torch.Tensor, out_ref: torch.Tensor, exact: bool) -> None:
+    """out_h / out_ref: uint8 code tensors on the CPU."""
+    if exact:
+        assert torch.equal(out_h, out_ref)
+        return
+    diff = (out_h.to(torch.int32) - out_ref.to(torch.int32)).abs()
+    differing = int((diff > 0).sum())
+    assert differing == 0 or int(diff.max()) == 1, f'codes more than one step apart (max {int(diff.max())})'
+    assert differing <= max(1, int(1e-4 * diff.numel())), f'{differing} of {diff.numel()} codes differ'
+    _totals['codes'] += diff.numel()
+    _totals['differing'] += differing
+    _totals['cases'] += 1
 
 
 def _routing(num_tokens, g):
@@ -60,8 +82,9 @@ def test_swiglu_forward_and_per_token_cast(oracle, cuda_device, num_tokens, hidd
 
     x = x_cpu.to(cuda_device)
     sm_total = config.get_device_num_sms()
-    for num_sms in (sm_total - 20, sm_total):
+    for num_sms, exact in ((sm_total - 20, False), (sm_total, False), (sm_total, True)):
         config.set_num_sms(num_sms)
+        config.set_exact_swiglu_codes(exact)
         counts = torch.zeros(3, dtype=torch.int64, device=cuda_device) if count else None
         out, sf = quant.swiglu_forward_and_per_token_cast(
             x, 'e4m3', g,
@@ -70,9 +93,11 @@ def test_swiglu_forward_and_per_token_cast(oracle, cuda_device, num_tokens, hidd
             pos_to_expert=pos_to_expert.to(cuda_device) if masked else None,
             use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue,
             swiglu_clamp_value=clamp, clamped_count=counts)
+        config.set_exact_swiglu_codes(False)
         # skipped rows are left unwritten by the kernel: blank them on both sides before comparing
         out_h = to_host(out).view(torch.uint8).masked_fill(mask, 0)
-        assert torch.equal(out_h, out_ref.view(torch.uint8).masked_fill(mask, 0))
+        approximate = not exact and dtype == torch.bfloat16 and g == 128 and hidden >= 1024
+        _check_codes(out_h, out_ref.view(torch.uint8).masked_fill(mask, 0), exact=not approximate)
         sf_h, sf_r = to_host(sf).clone(), sf_ref.clone()
         sf_h[mask.expand_as(sf_h)] = 0
         sf_r[mask.expand_as(sf_r)] = 0
@@ -81,14 +106,81 @@ def test_swiglu_forward_and_per_token_cast(oracle, cuda_device, num_tokens, hidd
             assert torch.equal(counts.cpu(), counts_ref)
 
 
-def test_custom_sf_clamp_min(oracle, cuda_device):
+def test_overall_code_difference_rate():
+    """Over every approximate case above together: far below the 1e-4 the rule allows."""
+    assert _totals['cases'] > 0 and _totals['codes'] > 10 ** 7
+    assert _totals['differing'] <= 1e-5 * _totals['codes'], _totals
+
+
+@pytest.mark.parametrize('hidden', [512, 2048])
+@pytest.mark.parametrize('clamp_min', [1e-2, 1e-20, 1e-35])
+def test_custom_sf_clamp_min(oracle, cuda_device, hidden, clamp_min):
+    """Custom clamps of the maximum, with rows small enough for the clamp to decide the scale.  A clamp below 1e-30
+    takes the exact kernel (the approximate one needs every decisive value to be a normal number)."""
     from tilekernels_b200 import quant
     gen = torch.Generator().manual_seed(3)
-    x_cpu = (torch.randn((130, 512), generator=gen) * 1e-3).to(torch.bfloat16)
-    out, sf = quant.swiglu_forward_and_per_token_cast(x_cpu.to(cuda_device), 'e4m3', 128, sf_clamp_min=1e-2)
-    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x_cpu), 'e4m3', (1, 128), clamp_min=1e-2)
-    assert_equal(to_host(out), out_ref)
+    x_cpu = (torch.randn((130, 2 * hidden), generator=gen) * 1e-3).to(torch.bfloat16)
+    x_cpu[5] *= 1e-12
+    x_cpu[6] *= 1e-19
+    x_cpu[7] = 0
+    out, sf = quant.swiglu_forward_and_per_token_cast(x_cpu.to(cuda_device), 'e4m3', 128, sf_clamp_min=clamp_min)
+    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x_cpu), 'e4m3', (1, 128), clamp_min=clamp_min)
     assert_equal(to_host(sf), sf_ref)
+    _check_codes(to_host(out).view(torch.uint8), out_ref.view(torch.uint8), exact=hidden < 1024 or clamp_min < 1e-30)
+
+
+def _adversarial_input(gen, kind: str) -> torch.Tensor:
+    """[256, 2 * 2048] bf16 inputs built to stress the choice of the exactly evaluated elements."""
+    T, H = 256, 2048
+    x = torch.randn((T, 2 * H), generator=gen)
+    if kind == 'ties':
+        # many equal or nearly equal (gate, up) pairs in every group: the two largest activations of a group are
+        # often within a few ulp of each other, in different lanes and in the same lane
+        base = torch.randn((T, H // 128, 1, 2), generator=gen).expand(T, H // 128, 128, 2) * 3
+        jitter = (torch.rand((T, H // 128, 128, 2), generator=gen) < 0.9).float()
+        pairs = base * (1 - jitter) + torch.randn((T, H // 128, 128, 2), generator=gen) * jitter
+        x = torch.cat([pairs[..., 0].reshape(T, H), pairs[..., 1].reshape(T, H)], dim=1)
+    elif kind == 'quantised':
+        # gates and ups on a coarse grid: a few hundred distinct activations per row, so exact ties abound
+        x = (x * 4).round() / 4
+    elif kind == 'negative_gates':
+        # gates between -100 and -60 (exp overflows or nearly so) next to ordinary ones, huge ups beside them
+        x[:, :H] = torch.where(torch.rand((T, H), generator=gen) < 0.05, -60 - 40 * torch.rand((T, H), generator=gen), x[:, :H])
+        x[:, H:] *= torch.where(torch.rand((T, H), generator=gen) < 0.02, 1e20, 1.0)
+        x[3, :H] = -85.0
+        x[4, :H] = -95.0
+    elif kind == 'tiny':
+        x[:, :H] *= 10.0 ** (-30 * torch.rand((T, 1), generator=gen))
+        x[:, H:] *= 10.0 ** (-8 * torch.rand((T, 1), generator=gen))
+        x[9] = 0
+        x[10, :H] = 0
+    elif kind == 'large':
+        x[:, :H] *= 20
+        x[:, H:] *= 1e4
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize('flags', [(False, False, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('clamp', [None, 7.0])
+@pytest.mark.parametrize('kind', ['ties', 'quantised', 'negative_gates', 'tiny', 'large'])
+def test_exact_scales_on_adversarial_inputs(oracle, cuda_device, kind, clamp, flags):
+    """The approximate kernel's scales must equal the exactly evaluated ones whatever the data: near-ties between
+    the largest activations of a group, gates where the hardware exp overflows, tiny and huge values."""
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    gen = torch.Generator().manual_seed(len(kind) * 7 + (clamp is not None))
+    x_cpu = _adversarial_input(gen, kind)
+    out, sf = quant.swiglu_forward_and_per_token_cast(x_cpu.to(cuda_device), 'e4m3', 128, use_tma_aligned_col_major_sf=col,
+                                                      round_sf=rnd, use_packed_ue8m0=ue, swiglu_clamp_value=clamp)
+    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x_cpu, swiglu_clamp_value=clamp), 'e4m3', (1, 128),
+                                  use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue)
+    assert_equal(to_host(sf), sf_ref)
+    diff = (to_host(out).view(torch.uint8).to(torch.int32) - out_ref.view(torch.uint8).to(torch.int32)).abs()
+    # data built from few distinct values repeats whatever code an approximation moves, so only the step is bounded
+    # here for those; the random kinds keep the 1e-4 rule
+    assert int(diff.max()) <= 1
+    if kind in ('negative_gates', 'tiny', 'large'):
+        assert int((diff > 0).sum()) <= max(1, int(1e-4 * diff.numel()))
 
 
 @pytest.mark.parametrize('clamp', [None, 10.0, 0.5, 0.3])

@@ -9,7 +9,7 @@ LIB_PATH = os.environ.get('TKQ_LIB_PATH') or os.path.join(_HERE, 'lib', 'libtkqu
 # enums of include/tkquant.h
 DT_BF16, DT_FP32 = 0, 1
 FMT_E4M3, FMT_E2M1, FMT_E5M6 = 0, 1, 2
-ROUND_SF, SF_COL_MAJOR, SF_UE8M0, SF_ONLY, CAST_ONLY = 1, 2, 4, 8, 16
+ROUND_SF, SF_COL_MAJOR, SF_UE8M0, SF_ONLY, CAST_ONLY, EXACT_CODES = 1, 2, 4, 8, 16, 32
 
 _vp, _i64, _int, _uint, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint, ctypes.c_float
 
@@ -17,6 +17,7 @@ _vp, _i64, _int, _uint, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ct
 SIGNATURES = {
     'tkq_version': [],
     'tkq_device_error': [],
+    'tkq_selftest_bounded_wait': [_vp, _uint, _vp, _vp],
     'tkq_per_token_cast': [_vp, _int, _i64, _i64, _i64, _int, _i64, _uint, _vp, _vp, _i64, _vp],
     'tkq_per_token_cast_quantized': [_vp, _int, _vp, _uint, _i64, _int, _int, _i64, _i64, _i64, _int, _i64, _uint, _vp, _vp, _i64,
                                      _vp],

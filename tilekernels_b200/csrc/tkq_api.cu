@@ -34,24 +34,58 @@ int device_sm_count() {
     return n;
 }
 
+static int current_device() {
+    int dev = 0;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+
 int cached_occupancy(const void* kernel, int threads, int dyn_smem) {
     struct Entry {
         const void* kernel;
-        int threads, smem, occ;
+        int device, threads, smem, occ;
     };
-    static Entry table[256];
+    static Entry table[512];
     static int used = 0;
     static std::mutex mu;
+    const int dev = current_device();
     std::lock_guard<std::mutex> lock(mu);
     for (int i = 0; i < used; ++i)
-        if (table[i].kernel == kernel && table[i].threads == threads && table[i].smem == dyn_smem) return table[i].occ;
+        if (table[i].kernel == kernel && table[i].device == dev && table[i].threads == threads && table[i].smem == dyn_smem)
+            return table[i].occ;
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, dyn_smem) != cudaSuccess || occ < 1) {
         cudaGetLastError();
         occ = 1;
     }
-    if (used < 256) table[used++] = Entry{kernel, threads, dyn_smem, occ};
+    if (used < 512) table[used++] = Entry{kernel, dev, threads, dyn_smem, occ};
     return occ;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+    struct Entry {
+        const void* kernel;
+        int device, bytes;
+    };
+    static Entry table[512];
+    static int used = 0;
+    static std::mutex mu;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(mu);
+    int slot = -1;
+    for (int i = 0; i < used; ++i)
+        if (table[i].kernel == kernel && table[i].device == dev) {
+            if (table[i].bytes >= bytes) return 0;
+            slot = i;
+            break;
+        }
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
+    }
+    if (slot >= 0) table[slot].bytes = bytes;
+    else if (used < 512) table[used++] = Entry{kernel, dev, bytes};  // a full table only costs the repeated call
+    return 0;
 }
 
 }  // namespace tkq

@@ -19,10 +19,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// Bounded wait: returns false if the phase did not complete within the poll limit (seconds).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: returns false if the phase did not complete within `limit` polls (the default is seconds long).
+// A kernel whose wait fails raises its failure flag and returns; what it has written by then is undefined.
+constexpr uint32_t kDefaultPollLimit = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kDefaultPollLimit) {
     const uint32_t addr = smem_u32(bar);
-    for (int i = 0; i < (1 << 22); ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
@@ -77,5 +80,6 @@ __device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap*
 // Each translation unit with waiting kernels keeps its own failure flag; these read and clear them.
 int tile_wait_flag();
 int row_wait_flag();
+int swiglu_wait_flag();
 
 }  // namespace tkq

@@ -10,8 +10,13 @@ namespace tkq {
 // Grid for a grid-stride kernel: enough blocks to fill every SM at the kernel's
 // own occupancy (whole waves over the SM count), never more than the work needs.
 // The occupancy query is cached per kernel instance and block size.
-// Resident blocks per SM of `kernel` at this block size (cached; tkq_api.cu).
+// Resident blocks per SM of `kernel` at this block size on the current device (cached per device; tkq_api.cu).
 int cached_occupancy(const void* kernel, int threads, int dyn_smem);
+
+// Raises the kernel's dynamic shared-memory limit to at least `bytes` on the current device.  The attribute
+// belongs to the (device, kernel) pair, so the cache that avoids repeating the call is keyed by both.
+// Returns 0 or the code set_error recorded.
+int ensure_dynamic_smem(const void* kernel, int bytes);
 
 template <class Kernel>
 int grid_size(Kernel kernel, int threads, int64_t blocks_of_work, int dyn_smem, int sm_limit = 0) {

@@ -63,12 +63,7 @@ template <int DT, int K>
 static int launch_e5m6_pipeline(const TokenCastParams& p, int threads, uint32_t stages, uint32_t stage_bytes, cudaStream_t stream) {
     auto kernel = e5m6_row_pipeline_kernel<DT, K>;
     const int smem = static_cast<int>(stages * stage_bytes);
-    static thread_local decltype(kernel) configured = nullptr;
-    if (configured != kernel) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
-        configured = kernel;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 200 * 1024)) return rc;
     const int grid = grid_size(kernel, threads, p.num_tokens, smem);
     kernel<<<grid, threads, smem, stream>>>(p, stages, stage_bytes);
     return check_launch("per_token_cast_e5m6 (row pipeline)");

@@ -2,9 +2,43 @@
 #include <cstring>
 
 #include "tkq_launch.cuh"
+#include "tkq_swiglu_pipeline.cuh"
 #include "tkq_token_kernels.cuh"
 
 namespace tkq {
+
+// The staged kernel with approximate codes and exact scales (tkq_swiglu_pipeline.cuh): bf16 rows of at least 1024
+// activations, scale groups of 128, a clamp of the maximum that keeps every decisive value a normal number.
+static bool pipeline_applies(const TokenCastParams& p, int in_dtype, bool per_row_scale, unsigned flags) {
+    return in_dtype == TKQ_DT_BF16 && !per_row_scale && p.hidden >= 1024 && p.clamp_min >= 1e-30f && !(flags & TKQ_EXACT_CODES);
+}
+
+template <int kClampMode>
+static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t stream) {
+    auto kernel = swiglu_group_pipeline_kernel<kClampMode>;
+    const int64_t nseg = (p.hidden + kSwSegment - 1) / kSwSegment;
+    const int64_t total = p.num_tokens * nseg;
+    if (total >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "more than 2^31 work items; split the token dimension");
+    constexpr int kStages = 3;
+    const int smem = kStages * kSwStageBytes;
+    p.total_items = static_cast<uint32_t>(total);
+    const int grid = grid_size(kernel, kSwThreads, total, smem, sm_limit);
+    kernel<<<grid, kSwThreads, smem, stream>>>(p, static_cast<uint32_t>(nseg), kStages);
+    return check_launch("swiglu_forward_and_per_token_cast (staged kernel)");
+}
+
+static int dispatch_swiglu_pipeline(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
+    if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0>(p, sm_limit, stream);
+    if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1>(p, sm_limit, stream);
+    return launch_swiglu_pipeline<2>(p, sm_limit, stream);
+}
+
+int swiglu_wait_flag() {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_swiglu_wait_failed, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_swiglu_wait_failed, &zero, sizeof(zero));
+    return static_cast<int>(v);
+}
 
 template <int DT, int kClampMode>
 static int launch_swiglu_group(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
@@ -57,6 +91,8 @@ extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype
         return set_error(TKQ_E_BAD_ARG, "swiglu cast: pos_to_token_topk and topk_weights go together");
     if (clamped_count != nullptr && swiglu_clamp < 0.0f)
         return set_error(TKQ_E_BAD_ARG, "swiglu cast: clamped_count needs a clamp value");
+    if (flags & ~(TKQ_ROUND_SF | TKQ_SF_COL_MAJOR | TKQ_SF_UE8M0 | TKQ_SF_ONLY | TKQ_CAST_ONLY | TKQ_EXACT_CODES))
+        return set_error(TKQ_E_BAD_ARG, "swiglu cast: unknown flag bit");
     if (flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY)) return set_error(TKQ_E_UNSUPPORTED, "swiglu cast: sf-only / cast-only not defined");
     if ((flags & TKQ_SF_UE8M0) && !(flags & TKQ_SF_COL_MAJOR))
         return set_error(TKQ_E_UNSUPPORTED, "packed ue8m0 scales need the column-major layout");
@@ -77,7 +113,7 @@ extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype
     p.out_stride = hidden;
     p.num_tokens = num_tokens;
     p.hidden = hidden;
-    p.flags = flags;
+    p.flags = flags & ~TKQ_EXACT_CODES;
     p.clamp_min = sf_clamp_min < 0.0f ? 1e-4f : sf_clamp_min;
     p.wide_loads = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && ((hidden * elem) % 32 == 0);
     p.pos_to_token_topk = pos_to_token_topk;
@@ -94,6 +130,7 @@ extern "C" int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype
     p.fast_pow2 = can_use_fast_pow2(flags, p.clamp_min, 448.0f);
     const int sm_limit = clamped_count != nullptr ? num_sms : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (pipeline_applies(p, in_dtype, per_row_scale, flags)) return dispatch_swiglu_pipeline(p, sm_limit, s);
     return in_dtype == TKQ_DT_BF16 ? dispatch_clamp<TKQ_DT_BF16>(p, per_row_scale, sm_limit, s)
                                    : dispatch_clamp<TKQ_DT_FP32>(p, per_row_scale, sm_limit, s);
 }

@@ -25,6 +25,8 @@ constexpr int kTileThreads = 256;
 
 // Set when a kernel gave up waiting for its tile; read back by tkq_device_error().
 __device__ unsigned int g_tile_wait_failed = 0;
+// Number of (row, 16-value chunk) pieces whose input scale the lossless re-blocking could not represent exactly.
+__device__ unsigned int g_lossless_range_violations = 0;
 
 struct TileParams {
     const void* x;
@@ -122,6 +124,9 @@ __device__ __forceinline__ void run_tile_pipeline_rw(const TileParams& p, const 
         const TileCoord c = tile_coord(p, first + i * step);
         if (!mbar_wait(full_bar + s, parity)) {
             atomicExch(&g_tile_wait_failed, 1u);
+            if (t == 0) {  // tiles requested ahead still target this block's shared memory: wait for them (bounded) too
+                for (uint32_t j = i + 1; j < my_tiles && j < i + stages; ++j) mbar_wait(full_bar + j % stages, (j / stages) & 1);
+            }
             return;
         }
         read(smem + static_cast<size_t>(s) * TileElem<DT>::kTileBytes, c);
@@ -718,7 +723,9 @@ __global__ void __launch_bounds__(kTileThreads) per_block_cast_lossless_kernel(c
         if (col_ok && r < valid_rows) {
             const int m = exp_max[(r / p.out_bm) * ncb + cb];
             const uint32_t e_out = m >= 6 ? m - 6 : 0;
-            const float rel = __uint_as_float((e_in[k] - e_out + 127u) << 23);  // 2^(e_in - e_out)
+            // where the reference asserts on the device (e_in + 5 >= e_out, exact representability), count and carry on
+            if (e_in[k] + 5u < e_out) atomicAdd(&g_lossless_range_violations, 1u);
+            const float rel = e_in[k] + 127u > e_out ? __uint_as_float((e_in[k] - e_out + 127u) << 23) : 0.0f;  // 2^(e_in - e_out)
             float v[16];
             QuantSource<TKQ_FMT_E2M1>::unpack(raw[k], v, rel);
             stg128(p.in.out + (row0 + r) * hidden + col0 + c16 * 16, cvt_e4m3x4(v[0], v[1], v[2], v[3]), cvt_e4m3x4(v[4], v[5], v[6], v[7]),
@@ -773,12 +780,7 @@ static int launch_tile(Kernel kernel, TileParams p, int elem_bytes, const char* 
     p.num_tiles = static_cast<uint32_t>(tiles);
     p.stages = static_cast<uint32_t>(stages);
     const int smem = stages * tile_bytes;
-    static thread_local Kernel configured = nullptr;
-    if (configured != kernel) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
-        configured = kernel;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), 100 * 1024)) return rc;
     kernel<<<grid, kTileThreads, smem, stream>>>(tmap, p);
     return check_launch(what);
 }
@@ -793,12 +795,7 @@ static int launch_tile_light(Kernel kernel, TileParams p, const char* what, cuda
     alignas(64) CUtensorMap tmap;
     if (int rc = make_tensor_map(&tmap, p.x, elem_bytes, p.num_tokens, p.hidden)) return rc;
     const int smem = TileElem<DT>::kTileBytes;
-    static thread_local Kernel configured = nullptr;
-    if (configured != kernel) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error(static_cast<int>(e), "cudaFuncSetAttribute(max dynamic shared memory) failed");
-        configured = kernel;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
     p.num_tiles = static_cast<uint32_t>(tiles);
     p.stages = 1;
     const int grid = grid_size(kernel, kTileThreads, tiles, smem);
@@ -950,10 +947,53 @@ int tkq::tile_wait_flag() {
     return static_cast<int>(v);
 }
 
+static int lossless_violation_flag() {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_lossless_range_violations, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_lossless_range_violations, &zero, sizeof(zero));
+    return v ? 1 : 0;
+}
+
 extern "C" int tkq_device_error(void) {
-    const int a = tile_wait_flag(), b = row_wait_flag();
-    if (a < 0 || b < 0) return -1;
-    return (a | b) ? 1 : 0;
+    const int a = tile_wait_flag(), b = row_wait_flag(), c = swiglu_wait_flag(), d = lossless_violation_flag();
+    if (a < 0 || b < 0 || c < 0 || d < 0) return -1;
+    return ((a | b | c) ? TKQ_DEVICE_WAIT_TIMEOUT : 0) | (d ? TKQ_DEVICE_LOSSLESS_RANGE : 0);
+}
+
+namespace tkq {
+// Self-test of the bounded wait: one bulk copy of 16 bytes arrives on the first barrier (waited for with the
+// default limit, so nothing is in flight afterwards); nothing ever arrives on the second one, and the wait on it
+// gives up after `limit` polls, raises the flag and returns.
+__global__ void bounded_wait_probe_kernel(const uint8_t* src, uint32_t limit, uint32_t* echo) {
+    __shared__ __align__(16) uint8_t buf[16];
+    __shared__ uint64_t bar[2];
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        mbar_init(bar + 1, 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(bar, 16);
+        bulk_load(buf, src, 16, bar);
+    }
+    if (!mbar_wait(bar, 0)) {
+        atomicExch(&g_tile_wait_failed, 1u);
+        return;
+    }
+    if (threadIdx.x == 0 && echo != nullptr) *echo = *reinterpret_cast<const uint32_t*>(buf);
+    if (!mbar_wait(bar + 1, 0, limit)) {
+        atomicExch(&g_tile_wait_failed, 1u);
+        return;
+    }
+}
+}  // namespace tkq
+
+extern "C" int tkq_selftest_bounded_wait(const void* src16, unsigned poll_limit, void* echo, void* stream) {
+    if (src16 == nullptr || !aligned16(src16) || poll_limit == 0 || poll_limit > (1u << 16))
+        return set_error(TKQ_E_BAD_ARG, "selftest_bounded_wait: 16-byte aligned source, poll limit in 1..65536");
+    bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(src16), poll_limit,
+                                                                               static_cast<uint32_t*>(echo));
+    return check_launch("selftest_bounded_wait");
 }
 
 extern "C" int tkq_per_block_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden, int fmt, int block_m,

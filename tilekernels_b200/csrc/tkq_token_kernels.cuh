@@ -438,7 +438,12 @@ __global__ void __launch_bounds__(kRowMaxThreads) e5m6_row_pipeline_kernel(const
         uint8_t* stage = ring + static_cast<size_t>(s) * stage_bytes;
         if (!mbar_wait(full_bar + s, static_cast<uint32_t>(i / stages) & 1u)) {
             atomicExch(&g_row_wait_failed, 1u);
-            if (t == 0) bulk_store_wait_all();  // rows already handed to the store engine still read this block's ring
+            if (t == 0) {
+                bulk_store_wait_all();  // rows already handed to the store engine still read this block's ring
+                // rows requested ahead still target this block's ring: wait for them (bounded) before the block ends
+                for (int64_t j = i + 1; j < my_rows && j < i + stages - 1; ++j)
+                    mbar_wait(full_bar + static_cast<uint32_t>(j % stages), static_cast<uint32_t>(j / stages) & 1u);
+            }
             return;
         }
         // the thread's K chunks of 16 values

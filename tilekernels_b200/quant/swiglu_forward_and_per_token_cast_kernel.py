@@ -5,7 +5,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from ..config import get_num_sms
+from ..config import get_exact_swiglu_codes, get_num_sms
 from .common import DTYPE_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_output_config
 from .types import QuantTensor
 
@@ -78,7 +78,7 @@ def swiglu_forward_and_per_token_cast(
                 None if clamped_count is None else clamped_count.data_ptr(),
                 -1.0 if sf_clamp_min is None else float(sf_clamp_min),
                 get_num_sms() if clamped_count is not None else 0,
-                out_config.flags, out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))
+                out_config.flags | (_lib.EXACT_CODES if get_exact_swiglu_codes() else 0), out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))
         _lib.check(rc, 'tkq_swiglu_forward_and_per_token_cast')
 
     out_sf = cast_epilogue(out_sf, num_expanded_tokens, hidden, out_config)
