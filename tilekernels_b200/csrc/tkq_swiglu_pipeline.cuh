@@ -1,10 +1,11 @@
 // Fused SwiGLU + per-token e4m3 cast (scale groups of 128), bf16 input, rows staged by the bulk-copy engine.
 //
-// Work item: one row segment of up to 2048 activations (128 threads x 16).  Thread 0 keeps `stages` items in
-// flight, each as two cp.async.bulk copies (the gate columns and the up columns of the segment) into a ring of
-// shared-memory stages that complete on one mbarrier per stage; all threads then compute from shared memory and
-// write codes and scales straight to global memory.  Bytes in flight therefore do not depend on registers or on
-// the number of resident warps.
+// Work item: one row segment of up to 2048 activations; a block is 64 threads and every thread owns two chunks of
+// 16 activations of it (chunk t and chunk t + 64), so the per-item bookkeeping is paid once per 32 activations.
+// Thread 0 keeps `stages` items in flight, each as two cp.async.bulk copies (the gate columns and the up columns
+// of the segment) into a ring of shared-memory stages that complete on one mbarrier per stage; all threads then
+// compute from shared memory and write codes and scales straight to global memory.  Bytes in flight therefore do
+// not depend on registers or on the number of resident warps.
 //
 // Arithmetic.  The reference evaluates y = g / (1 + exp(-g)) * u in fp32 and derives the scale of a group from
 // max |y| (tile_kernels/quant/swiglu_forward_and_per_token_cast_kernel.py:140-160).  A reproducible exp and a
@@ -13,12 +14,13 @@
 //   * every activation is evaluated once with ex2.approx / rcp.approx (relative error below 2^-18 for gates
 //     >= -80): these values become the FP8 codes, so a code can differ from the exactly evaluated one only when
 //     the scaled activation lies within that error of a rounding boundary;
-//   * the group maximum, which fixes the scale, is evaluated EXACTLY: every lane whose approximate values come
-//     within 2^-15 of the group's approximate maximum is "flagged" (normally one lane per group: the one that
-//     holds the maximum), the 16 (gate, up) pairs of a flagged lane are evaluated again by the 8 lanes of the
-//     group, two pairs each, with the exact routine, and the group maximum is taken over those exact values.
-//     The margin is 8 times the error bound, so the exactly largest element is always among the re-evaluated
-//     ones and the scale equals the scale of a fully exact evaluation bit for bit;
+//   * the group maximum, which fixes the scale, is evaluated EXACTLY: every half chunk (8 values of one lane)
+//     whose approximate values come within 2^-15 of the group's approximate maximum is "flagged" (normally one
+//     per group: the one that holds the maximum); the 8 (gate, up) pairs of a flagged half chunk are evaluated
+//     again by the 8 lanes of the group, one pair each, with the exact routine -- as the two halves of one packed
+//     evaluation that serves the lane's first and second chunk at once -- and the group maximum is taken over
+//     those exact values.  The margin is 8 times the error bound, so the exactly largest element is always among
+//     the re-evaluated ones and the scale equals the scale of a fully exact evaluation bit for bit;
 //   * a lane that holds a gate below -80 (where ex2 overflows and the error bound is lost) sends its warp's
 //     whole step through the exact routine.
 #pragma once
@@ -28,9 +30,10 @@
 
 namespace tkq {
 
-constexpr int kSwThreads = 128;
-constexpr int kSwSegment = kSwThreads * 16;        // activations per work item
-constexpr int kSwHalfBytes = kSwSegment * 2;       // bytes of the gate (or up) part of a stage
+constexpr int kSwThreads = 64;
+constexpr int kSwChunks = 2;                              // chunks of 16 activations per thread and item
+constexpr int kSwSegment = kSwThreads * kSwChunks * 16;  // activations per work item
+constexpr int kSwHalfBytes = kSwSegment * 2;             // bytes of the gate (or up) part of a stage
 constexpr int kSwStageBytes = 2 * kSwHalfBytes;
 constexpr int kSwMaxStages = 4;
 
@@ -75,15 +78,115 @@ __device__ __noinline__ float swiglu_exact_element(float g, float u, float clamp
     return w != 1.0f ? __fmul_rn(v, w) : v;
 }
 
+// Maximum over the 8 lanes of a scale group.  (redux.sync with a sub-warp member mask was measured: it is emulated
+// and costs far more than these three shuffle + max steps.)
 __device__ __forceinline__ float group8_max(float m) {
     m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
     m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 2));
     return fmaxf(m, __shfl_xor_sync(kFullMask, m, 4));
 }
 
+// fp32 scale and inverse of the e4m3 cast without the two IEEE divisions, same bits:
+//   a / 448   = fma(fma(-448, q, a), c, q) with c = RN(1 / 448), q = a * c
+//   448 / a   = reciprocal approximation, one Newton step, quotient, exact residual, correction
+// Both were compared on the GPU with __fdiv_rn for all 2^23 mantissas of a over binades from 2^-100 to 2^110; the
+// caller guarantees 1e-30 <= a <= 2^100 (nothing under- or overflows there), other values take make_scale.
+__device__ __forceinline__ Scale make_scale_e4m3_nodiv(float amax, float clamp_min) {
+    Scale s;
+    const float a = fmaxf(amax, clamp_min);
+    const float c = 1.0f / 448.0f;
+    const float q = __fmul_rn(a, c);
+    s.sf = __fmaf_rn(__fmaf_rn(-448.0f, q, a), c, q);
+    float y = rcp_approx(a);
+    y = __fmaf_rn(y, __fmaf_rn(-a, y, 1.0f), y);
+    const float r = __fmul_rn(448.0f, y);
+    s.inv = __fmaf_rn(__fmaf_rn(-a, r, 448.0f), y, r);
+    s.e8 = __float_as_uint(s.sf) >> 23;
+    return s;
+}
+
+// 16 activations of one chunk, approximately: y = g * (r * u) with r = rcp(1 + ex2(-g * log2 e)), times the row
+// weight.  Returns the largest magnitudes of y[0..7] and y[8..15] and lowers g_min to the smallest gate.
+template <int kClampMode>
+__device__ __forceinline__ void swiglu_approx_chunk(const uint8_t* st, uint32_t chunk, bool active, float clamp, float w,
+                                                    ClampCounters& cnt, float* y, float& max_lo, float& max_hi, float& g_min) {
+    uint32_t G[8], U[8];
+    if (active) {
+        const uint4* gp = reinterpret_cast<const uint4*>(st + chunk * 32);
+        const uint4* up = reinterpret_cast<const uint4*>(st + kSwHalfBytes + chunk * 32);
+        const uint4 g0 = gp[0], g1 = gp[1], u0 = up[0], u1 = up[1];
+        G[0] = g0.x, G[1] = g0.y, G[2] = g0.z, G[3] = g0.w, G[4] = g1.x, G[5] = g1.y, G[6] = g1.z, G[7] = g1.w;
+        U[0] = u0.x, U[1] = u0.y, U[2] = u0.z, U[3] = u0.w, U[4] = u1.x, U[5] = u1.y, U[6] = u1.z, U[7] = u1.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) G[i] = U[i] = 0;
+    }
+    float g[16], u[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        g[2 * i] = bf16_lo(G[i]);
+        g[2 * i + 1] = bf16_hi(G[i]);
+        u[2 * i] = bf16_lo(U[i]);
+        u[2 * i + 1] = bf16_hi(U[i]);
+    }
+    if (kClampMode > 0) {
+        float g_hi = 0.0f, u_hi = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            g_hi = max3(g_hi, g[i], g[i + 1]);
+            u_hi = max3_abs(u_hi, u[i], u[i + 1]);
+        }
+        if (g_hi > clamp || u_hi > clamp) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (kClampMode > 1) {
+                    cnt.gate_hi += g[i] > clamp;
+                    cnt.up_hi += u[i] > clamp;
+                    cnt.up_lo += u[i] < -clamp;
+                }
+                g[i] = g[i] > clamp ? clamp : g[i];
+                u[i] = u[i] > clamp ? clamp : u[i];
+                u[i] = u[i] < -clamp ? -clamp : u[i];
+            }
+        }
+    }
+    float g_min_b = 0.0f;  // two chains of four: less waiting on the previous result
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        g_min = min3(g_min, g[i], g[i + 1]);
+        g_min_b = min3(g_min_b, g[8 + i], g[8 + i + 1]);
+    }
+    g_min = fminf(g_min, g_min_b);
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        const float2 g2 = make_float2(g[i], g[i + 1]);
+        const float2 e2 = mul2(g2, splat2(-1.4426950408889634f));
+        const float2 d2 = add2(make_float2(ex2_approx(e2.x), ex2_approx(e2.y)), splat2(1.0f));
+        const float2 r2 = make_float2(rcp_approx(d2.x), rcp_approx(d2.y));
+        // g * (r * u): r * u can only lose bits to underflow where the product is far below any clamp
+        const float2 v2 = mul2(g2, mul2(r2, make_float2(u[i], u[i + 1])));
+        y[i] = v2.x;
+        y[i + 1] = v2.y;
+    }
+    if (w != 1.0f) {  // uniform over the row
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            const float2 v2 = mul2(make_float2(y[i], y[i + 1]), splat2(w));
+            y[i] = v2.x;
+            y[i + 1] = v2.y;
+        }
+    }
+    max_lo = max_hi = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        max_lo = max3_abs(max_lo, y[i], y[i + 1]);
+        max_hi = max3_abs(max_hi, y[8 + i], y[8 + i + 1]);
+    }
+}
+
 // kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count
 template <int kClampMode>
-__global__ void __launch_bounds__(kSwThreads, 8)
+__global__ void __launch_bounds__(kSwThreads, 12)
 swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const uint32_t stages) {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full_bar[kSwMaxStages];
@@ -95,9 +198,13 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
     const bool col_major = p.flags & TKQ_SF_COL_MAJOR;
     const bool ue8m0 = p.flags & TKQ_SF_UE8M0;
     const bool bf16_gates = p.bf16_gates;
+    const bool fast_pow2 = p.fast_pow2;
     const float clamp = p.swiglu_clamp;
+    const float clamp_min = p.clamp_min;
     // values below half the clamp of the maximum cannot decide a scale: no exact evaluation for them
-    const float thr_floor = __fmul_rn(p.clamp_min, 0.5f);
+    const float thr_floor = __fmul_rn(clamp_min, 0.5f);
+    // fp32 scales: element strides of the token and the group index
+    const int64_t sf_token_stride = col_major ? 1 : p.sf_stride, sf_group_stride = col_major ? p.sf_stride : 1;
     ClampCounters cnt;
 
     if (t == 0) {
@@ -109,7 +216,7 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
     uint32_t p_item = blockIdx.x, p_loads = 0, p_stage = 0;
     auto produce = [&](uint32_t limit) {
         while (p_loads < limit && p_item < total) {
-            const uint32_t row = p_item / nseg, seg = p_item - row * nseg;
+            const uint32_t row = nseg == 1 ? p_item : p_item / nseg, seg = p_item - row * nseg;
             if (p.pos_to_expert == nullptr || p.pos_to_expert[row] >= 0) {
                 const uint32_t col0 = seg * kSwSegment;
                 const uint32_t bytes = min(static_cast<uint32_t>(kSwSegment), hidden - col0) * 2u;
@@ -128,7 +235,7 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
 
     uint32_t loads = 0, stage = 0, phase = 0;
     for (uint32_t item = blockIdx.x; item < total; item += gridDim.x) {
-        const uint32_t row = item / nseg, seg = item - row * nseg;
+        const uint32_t row = nseg == 1 ? item : item / nseg, seg = item - row * nseg;
         if (p.pos_to_expert != nullptr && p.pos_to_expert[row] < 0) continue;  // block-uniform
         // every thread is done with the stage of the previous load (its reads ordered before the refill)
         fence_proxy_async_smem();
@@ -148,140 +255,123 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
             return;
         }
         ++loads;
-        const uint32_t this_stage_next = stage + 1 == stages ? 0 : stage + 1;
-        phase ^= this_stage_next == 0 ? 1u : 0u;
-        stage = this_stage_next;
+        stage = stage + 1 == stages ? 0 : stage + 1;
+        phase ^= stage == 0 ? 1u : 0u;
 
-        const uint32_t col = seg * kSwSegment + t * 16;
-        if (col - lane * 16 >= hidden) continue;  // warp-uniform: this warp's 512 columns lie beyond the row
-        const bool active = col < hidden;          // whole groups of 8 lanes are active or not
-
-        uint32_t G[8], U[8];
-        if (active) {
-            const uint4* gp = reinterpret_cast<const uint4*>(st + t * 32);
-            const uint4* up = reinterpret_cast<const uint4*>(st + kSwHalfBytes + t * 32);
-            const uint4 g0 = gp[0], g1 = gp[1], u0 = up[0], u1 = up[1];
-            G[0] = g0.x, G[1] = g0.y, G[2] = g0.z, G[3] = g0.w, G[4] = g1.x, G[5] = g1.y, G[6] = g1.z, G[7] = g1.w;
-            U[0] = u0.x, U[1] = u0.y, U[2] = u0.z, U[3] = u0.w, U[4] = u1.x, U[5] = u1.y, U[6] = u1.z, U[7] = u1.w;
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) G[i] = U[i] = 0;
-        }
+        const uint32_t seg_col = seg * kSwSegment;
+        const uint32_t width = min(static_cast<uint32_t>(kSwSegment), hidden - seg_col);  // a multiple of 128
+        if ((t & ~31u) * 16 >= width) continue;  // warp-uniform: even this warp's first chunks lie beyond the row
         float w = 1.0f;
         if (p.pos_to_token_topk != nullptr) {
             const int32_t pos = p.pos_to_token_topk[row];
             w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
         }
 
-        // --- approximate evaluation of the lane's 16 activations ---
-        float y[16];
+        // --- approximate evaluation of the thread's two chunks (whole groups of 8 lanes are active or not) ---
+        float y[kSwChunks][16], max_lo[kSwChunks], max_hi[kSwChunks];
+        bool active[kSwChunks];
         float g_min = 0.0f;
-        {
-            float g[16], u[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                g[2 * i] = bf16_lo(G[i]);
-                g[2 * i + 1] = bf16_hi(G[i]);
-                u[2 * i] = bf16_lo(U[i]);
-                u[2 * i + 1] = bf16_hi(U[i]);
-            }
-            if (kClampMode > 0) {
-                float g_hi = 0.0f, u_hi = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    g_hi = max3(g_hi, g[i], g[i + 1]);
-                    u_hi = max3_abs(u_hi, u[i], u[i + 1]);
-                }
-                if (g_hi > clamp || u_hi > clamp) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if (kClampMode > 1) {
-                            cnt.gate_hi += g[i] > clamp;
-                            cnt.up_hi += u[i] > clamp;
-                            cnt.up_lo += u[i] < -clamp;
-                        }
-                        g[i] = g[i] > clamp ? clamp : g[i];
-                        u[i] = u[i] > clamp ? clamp : u[i];
-                        u[i] = u[i] < -clamp ? -clamp : u[i];
-                    }
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 16; i += 2) g_min = min3(g_min, g[i], g[i + 1]);
-#pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                const float2 g2 = make_float2(g[i], g[i + 1]);
-                const float2 e2 = mul2(g2, splat2(-1.4426950408889634f));
-                const float2 d2 = add2(make_float2(ex2_approx(e2.x), ex2_approx(e2.y)), splat2(1.0f));
-                const float2 r2 = make_float2(rcp_approx(d2.x), rcp_approx(d2.y));
-                // g * (r * u): r * u can only lose bits to underflow where the product is far below any clamp
-                const float2 v2 = mul2(g2, mul2(r2, make_float2(u[i], u[i + 1])));
-                y[i] = v2.x;
-                y[i + 1] = v2.y;
-            }
-        }
-        if (w != 1.0f) {  // uniform over the row
-#pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                const float2 v2 = mul2(make_float2(y[i], y[i + 1]), splat2(w));
-                y[i] = v2.x;
-                y[i + 1] = v2.y;
-            }
+        for (int c = 0; c < kSwChunks; ++c) {
+            const uint32_t chunk = t + c * kSwThreads;
+            active[c] = chunk * 16 < width;
+            swiglu_approx_chunk<kClampMode>(st, chunk, active[c], clamp, w, cnt, y[c], max_lo[c], max_hi[c], g_min);
         }
 
-        float amax;
+        float amax[kSwChunks];
         if (__any_sync(kFullMask, g_min < -80.0f)) {
-            // rare: the whole step through the exact routine (the stage still holds the inputs)
-            const uint16_t* gs = reinterpret_cast<const uint16_t*>(st + t * 32);
-            const uint16_t* us = reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + t * 32);
+            // rare: both chunks through the exact routine (the stage still holds the inputs)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float gi = active ? __uint_as_float(static_cast<uint32_t>(gs[i]) << 16) : 0.0f;
-                const float ui = active ? __uint_as_float(static_cast<uint32_t>(us[i]) << 16) : 0.0f;
-                y[i] = swiglu_exact_element(gi, ui, kClampMode > 0 ? clamp : -1.0f, w);
-            }
-            amax = group8_max(absmax16(y));
-        } else {
-            // --- which lanes can hold the exact maximum of their group ---
-            const float approx_max = group8_max(absmax16(y));
-            const float thr = fmaxf(__fmaf_rn(approx_max, -3.0517578125e-05f, approx_max), thr_floor);
-            bool near_max = false;
+            for (int c = 0; c < kSwChunks; ++c) {
+                const uint32_t chunk = t + c * kSwThreads;
+                const uint16_t* gs = reinterpret_cast<const uint16_t*>(st + chunk * 32);
+                const uint16_t* us = reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + chunk * 32);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) near_max = near_max || (fabsf(y[i]) >= thr);
-            uint32_t todo = (__ballot_sync(kFullMask, near_max) >> (lane & 24u)) & 0xFFu;  // flagged lanes of my group
-            // --- their 16 pairs again, exactly: two pairs per lane of the group ---
-            float exact_max = 0.0f;
-            while (true) {
-                if (todo != 0) {
-                    const uint32_t holder = (t & ~7u) + (__ffs(todo) - 1);
-                    const uint32_t gw = *reinterpret_cast<const uint32_t*>(st + holder * 32 + (lane & 7u) * 4);
-                    const uint32_t uw = *reinterpret_cast<const uint32_t*>(st + kSwHalfBytes + holder * 32 + (lane & 7u) * 4);
-                    float2 g2 = make_float2(bf16_lo(gw), bf16_hi(gw));
-                    float2 u2 = make_float2(bf16_lo(uw), bf16_hi(uw));
-                    if (kClampMode > 0) {
-                        g2.x = g2.x > clamp ? clamp : g2.x;
-                        g2.y = g2.y > clamp ? clamp : g2.y;
-                        u2.x = fminf(fmaxf(u2.x, -clamp), clamp);
-                        u2.y = fminf(fmaxf(u2.y, -clamp), clamp);
-                    }
-                    float2 f2 = swiglu_exact2(g2, u2, bf16_gates);
-                    if (w != 1.0f) f2 = mul2(f2, splat2(w));
-                    exact_max = max3_abs(exact_max, f2.x, f2.y);
-                    todo &= todo - 1;
+                for (int i = 0; i < 16; ++i) {
+                    const float gi = active[c] ? __uint_as_float(static_cast<uint32_t>(gs[i]) << 16) : 0.0f;
+                    const float ui = active[c] ? __uint_as_float(static_cast<uint32_t>(us[i]) << 16) : 0.0f;
+                    y[c][i] = swiglu_exact_element(gi, ui, kClampMode > 0 ? clamp : -1.0f, w);
                 }
-                if (!__any_sync(kFullMask, todo != 0)) break;
+                amax[c] = group8_max(absmax16(y[c]));
             }
-            amax = group8_max(exact_max);
+        } else {
+            float approx_max[kSwChunks];
+            bool undecided = !fast_pow2;
+#pragma unroll
+            for (int c = 0; c < kSwChunks; ++c) {
+                approx_max[c] = group8_max(fmaxf(max_lo[c], max_hi[c]));
+                if (fast_pow2) {
+                    // a power-of-two scale only depends on the binade of the maximum and on whether its mantissa exceeds
+                    // 1.75: when both ends of the interval that must contain the exact maximum give the same exponent,
+                    // the scale is decided without any exact evaluation
+                    const float lo_end = fmaxf(__fmaf_rn(approx_max[c], -3.0517578125e-05f, approx_max[c]), clamp_min);
+                    const float hi_end = fmaxf(__fmaf_rn(approx_max[c], 3.0517578125e-05f, approx_max[c]), clamp_min);
+                    constexpr uint32_t kCarry = FmtTraits<TKQ_FMT_E4M3>::kMantCarry;
+                    undecided = undecided || ((__float_as_uint(lo_end) + kCarry) >> 23) != ((__float_as_uint(hi_end) + kCarry) >> 23);
+                }
+            }
+            if (!__any_sync(kFullMask, undecided)) {
+#pragma unroll
+                for (int c = 0; c < kSwChunks; ++c) amax[c] = approx_max[c];
+            } else {
+            // --- which half chunks can hold the exact maximum of their group: bit l = first half of lane l of the
+            //     group, bit 8 + l = its second half ---
+            uint32_t todo[kSwChunks];
+#pragma unroll
+            for (int c = 0; c < kSwChunks; ++c) {
+                const float thr = fmaxf(__fmaf_rn(approx_max[c], -3.0517578125e-05f, approx_max[c]), thr_floor);
+                const uint32_t lo = __ballot_sync(kFullMask, max_lo[c] >= thr), hi = __ballot_sync(kFullMask, max_hi[c] >= thr);
+                todo[c] = ((lo >> (lane & 24u)) & 0xFFu) | (((hi >> (lane & 24u)) & 0xFFu) << 8);
+            }
+            // --- their 8 pairs again, exactly: one pair per lane of the group, first chunk in .x, second in .y ---
+            float exact_max[kSwChunks] = {0.0f, 0.0f};
+            while (true) {
+                float gx[kSwChunks], ux[kSwChunks];
+#pragma unroll
+                for (int c = 0; c < kSwChunks; ++c) {
+                    gx[c] = 1.0f, ux[c] = 0.0f;  // nothing flagged: a pair whose activation is 0
+                    if (todo[c] != 0) {
+                        const uint32_t h = __ffs(todo[c]) - 1;
+                        const uint32_t off = ((t & ~7u) + (h & 7u) + c * kSwThreads) * 32 + (h >> 3) * 16 + (lane & 7u) * 2;
+                        gx[c] = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(st + off)) << 16);
+                        ux[c] = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + off)) << 16);
+                        todo[c] &= todo[c] - 1;
+                    }
+                }
+                float2 g2 = make_float2(gx[0], gx[1]), u2 = make_float2(ux[0], ux[1]);
+                if (kClampMode > 0) {
+                    g2.x = g2.x > clamp ? clamp : g2.x;
+                    g2.y = g2.y > clamp ? clamp : g2.y;
+                    u2.x = fminf(fmaxf(u2.x, -clamp), clamp);
+                    u2.y = fminf(fmaxf(u2.y, -clamp), clamp);
+                }
+                float2 f2 = swiglu_exact2(g2, u2, bf16_gates);
+                if (w != 1.0f) f2 = mul2(f2, splat2(w));
+                exact_max[0] = fmaxf(exact_max[0], fabsf(f2.x));
+                exact_max[1] = fmaxf(exact_max[1], fabsf(f2.y));
+                if (!__any_sync(kFullMask, (todo[0] | todo[1]) != 0)) break;
+            }
+#pragma unroll
+            for (int c = 0; c < kSwChunks; ++c) amax[c] = group8_max(exact_max[c]);
+            }
         }
 
-        const Scale sc = make_scale_for<TKQ_FMT_E4M3>(amax, p.clamp_min, round_sf, p.fast_pow2);
-        if (active) {
-            if ((lane & 7u) == 0) {
-                const uint32_t grp = col >> 7;
-                if (ue8m0) store_sf_ue8m0_byte(p.sf, p.sf_stride, row, grp, p.num_groups, sc.e8);
-                else store_sf_f32(p.sf, p.sf_stride, col_major, row, grp, sc.sf);
+        uint8_t* out_row = p.out + static_cast<int64_t>(row) * p.out_stride + seg_col;
+#pragma unroll
+        for (int c = 0; c < kSwChunks; ++c) {
+            const uint32_t chunk = t + c * kSwThreads;
+            Scale sc;
+            if (fast_pow2) sc = make_scale_pow2<TKQ_FMT_E4M3>(amax[c], clamp_min);
+            else if (!round_sf && amax[c] <= 1.2676506e30f) sc = make_scale_e4m3_nodiv(amax[c], clamp_min);
+            else sc = make_scale(amax[c], clamp_min, 448.0f, round_sf);
+            if (active[c]) {
+                if ((lane & 7u) == 0) {
+                    const uint32_t grp = (seg_col + chunk * 16) >> 7;
+                    if (ue8m0) store_sf_ue8m0_byte(p.sf, p.sf_stride, row, grp, p.num_groups, sc.e8);
+                    else static_cast<float*>(p.sf)[row * sf_token_stride + grp * sf_group_stride] = sc.sf;
+                }
+                quantize_store_e4m3x16(y[c], sc.inv, out_row + chunk * 16);
             }
-            quantize_store_e4m3x16(y, sc.inv, p.out + static_cast<int64_t>(row) * p.out_stride + col);
         }
     }
     if constexpr (kClampMode > 1) flush_clamp_counters(cnt, p.clamped_count);
