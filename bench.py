@@ -1,6 +1,6 @@
 """Benchmark of the quantization hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows R] [--no-ops]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows R] [--no-ops] [--records FILE]
 
 Workload ("cfg5"): per-token FP8 e4m3 cast, groups of 128, power-of-two scales packed as ue8m0 in the
 column-major layout, of a bf16 [262144, 7168] tensor ~ N(0,1) with 0.1% x100 outliers, token dimension
@@ -12,7 +12,9 @@ split evenly over the N ranks (no collective on the data path).  One step = one 
   roofline  algorithmic bytes (input + output + scales, each once) / kernel time against the measured
             HBM copy bandwidth of this pool (MEASURED_PEAKS.json, else the documented fallback)
   ops       (N = 1) the other benchmark workloads, each timed L2-cold by rotating over buffer sets
-            larger than twice the L2
+            larger than twice the L2, with a device copy of the same size and the host cost per call beside it;
+            --records FILE writes them as JSONL in the record form of the reference's benchmark plugin
+  shard_parity  every rank's first and last 4096-row band compared with the CPU checker (outside the timing)
   cpu_baseline  the CPU oracle (a C/OpenMP port of the reference's PyTorch path) on a bounded row sample
 
 --impl reference times that CPU port alone, on all host cores, as the reference arm.
@@ -34,10 +36,14 @@ HIDDEN = 7168
 GROUP = 128
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-# DRAM bytes per token of the dominant kernel from the ncu capture summarised in
-# profiles/per_token_cast_e4m3_ue8m0_cfg5.md: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch
-# over 32768 rows / 32768.  Traffic is proportional to the row count, so a launch's traffic is this x rows.
-NCU_DRAM_BYTES_PER_TOKEN = 20465
+TRAFFIC_FILE = os.path.join(ROOT, 'profiles', 'per_token_cast_e4m3_ue8m0_cfg5.traffic.json')
+
+
+def workload_config(total_rows: int, world: int) -> dict:
+    """The `config` object of the JSON line, the same for both arms."""
+    return {'workload': f'cfg5 per-token FP8 e4m3 cast, group 128, ue8m0 col-major scales, bf16 [{total_rows},{HIDDEN}]',
+            'rows_per_rank': total_rows // world, 'sharding': f'token dimension split over {world} rank(s), no collective',
+            'l2': 'inputs larger than L2 (no flush needed)'}
 
 
 def bytes_per_token() -> int:
@@ -52,6 +58,17 @@ def hbm_peak():
             return float(json.load(f)['hbm_gbs']), 'measured'
     except Exception:
         return FALLBACK_HBM_GBS, 'fallback'
+
+
+def profiled_traffic():
+    """DRAM bytes per token of the dominant kernel, from the last profiler capture of it (a small tracked JSON:
+    bytes read + written by one launch / its rows, and the commit the capture was taken at).  Traffic is
+    proportional to the row count, so a launch's traffic is this x rows.  None if the file is missing."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            return json.load(f)
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -161,27 +178,45 @@ def time_graph(torch, op, inputs, launches: int, replays: int = 7):
     return statistics.median(times), min(times)
 
 
-def bench_other_ops(torch, quant, device, count_bytes) -> list:
-    """cfg1-cfg4 on one GPU.  Working sets below the L2 size are timed L2-cold: each launch uses the next of
-    `sets` distinct input/output sets whose total size exceeds twice the L2."""
-    from tilekernels_b200 import moe
-    from tilekernels_b200.testing import make_config_input
-    peak, _ = hbm_peak()
-    specs = [
-        ('cfg1 per_token_cast e4m3 g128 fp32-sf [4096,7168]', 'cfg1', None, lambda x: quant.per_token_cast(x, 'e4m3', 128)),
-        ('cfg1 per_token_cast e4m3 g128 round_sf [4096,7168]', 'cfg1', None, lambda x: quant.per_token_cast(x, 'e4m3', 128, round_sf=True)),
-        ('cfg2 per_block_cast e4m3 128x128 [7168,2048]', 'cfg2', None, lambda x: quant.per_block_cast(x, 'e4m3', (128, 128))),
-        ('cfg2 per_channel_cast e4m3 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast(x, 'e4m3', 128)),
-        ('cfg3 swiglu_forward_and_per_token_cast e4m3 g128 [16384,4096]', 'cfg3', None,
-         lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128)),
-        ('cfg4 per_token_cast e2m1 g32 ue8m0 [32768,7168]', 'cfg4', None,
-         lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)),
-        ('cfg4 per_token_cast e5m6 [32768,7168]', 'cfg4', None, lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
-    ]
+def time_copy(torch, device, nbytes: int) -> float:
+    """Microseconds of a device-to-device copy that moves `nbytes` in total (reads nbytes / 2, writes nbytes / 2),
+    timed like the ops: CUDA-graph replay over rotating buffer pairs larger than twice the L2.  Two forms are timed
+    and the faster one is returned: Tensor.copy_ (the driver's memcpy, which may pick the copy engine) and an
+    elementwise kernel over 32-bit words (always on the SMs)."""
+    half = max(1024, nbytes // 2 // 1024 * 1024)
+    sets = max(2, -(-2 * L2_BYTES // (2 * half)) + 1)
+    srcs = [torch.empty(half // 4, dtype=torch.int32, device=device) for _ in range(sets)]
+    dsts = [torch.empty(half // 4, dtype=torch.int32, device=device) for _ in range(sets)]
+    pairs = list(zip(srcs, dsts))
+    memcpy, _ = time_graph(torch, lambda p: p[1].copy_(p[0]), pairs, launches=2 * sets)
+    kernel, _ = time_graph(torch, lambda p: torch.bitwise_or(p[0], 0, out=p[1]), pairs, launches=2 * sets)
+    return min(memcpy, kernel)
+
+
+def host_us_per_call(torch, op, x, calls: int = 1000) -> float:
+    """Wall-clock microseconds of one eager call of the Python entry point (asserts, output allocation, ctypes,
+    launch) on an input so small that the kernel itself does not matter."""
+    for _ in range(20):
+        op(x)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        op(x)
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    return (t1 - t0) / calls * 1e6
+
+
+def op_specs(torch, quant, moe, device) -> list:
+    """The per-op table: the benchmark workloads cfg1-cfg4, the steady-state shapes of the tile kernels and the rows
+    next to the hot path.  Each spec: kernel / operation / params (the record fields of the reference's benchmark
+    plugin, tests/pytest_benchmark_plugin.py:358-425), the workload tensor it starts from, an optional `prepare`
+    (workload tensor -> op input) and the op."""
     ue = dict(use_tma_aligned_col_major_sf=True, round_sf=True, use_packed_ue8m0=True)
     gather = torch.randint(0, 7168, (8192,), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
     gather[::11] = -1
-    gather = gather.to(device)
+    # row indices for the full workload and for the 128-row input of the host-cost measurement
+    gathers = {7168: gather.to(device), 128: torch.where(gather < 0, gather, gather % 128).to(device)}
 
     def backward_inputs(x):
         rows, hidden = x.shape[0], x.shape[1] // 2
@@ -193,38 +228,70 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         token_topk_to_pos[pos.long()] = torch.arange(rows, dtype=torch.int32)
         return (quant.per_token_cast(x, 'e4m3', 128, round_sf=True), grad_out, weight, pos.to(device), token_topk_to_pos.view(-1, 8).to(device))
 
-
     def expand_inputs(x):
         q, sf = quant.per_token_cast(x, 'e4m3', 128, None, **ue)
         positions = torch.randperm(x.shape[0] * 8, generator=torch.Generator().manual_seed(13)).to(torch.int32)
         return ((q, sf.contiguous()), positions.view(-1, 8).to(device), torch.zeros(x.shape[0] * 8, dtype=torch.int32, device=device))
 
-    # the rows next to the hot path (dequantisation, re-quantisation, fused / transposing per-channel casts):
-    # `prepare` turns the bf16 workload tensor into the op's input
-    specs += [
-        ('cfg4 per_token_cast_back e4m3 g128 ue8m0 -> bf16 [32768,7168]', 'cfg4', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, **ue),
-         lambda q: (quant.per_token_cast_back(q, 'bf16', 128),)),
-        ('cfg4 per_token_cast_back e5m6 -> bf16 [32768,7168]', 'cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1]),
-         lambda q: (quant.per_token_cast_back(q, 'bf16', 7168, x_special_fmt='e5m6'),)),
-        ('cfg4 per_token_cast e4m3 g128 of FP8 input with 128x128 ue8m0 scales [32768,7168]', 'cfg4',
-         lambda x: quant.per_block_cast(x, 'e4m3', (128, 128), **ue), lambda q: quant.per_token_cast(q, 'e4m3', 128, (128, 128), **ue)),
-        ('cfg2 per_channel_cast_fused bf16 + gather of 8192 rows [7168,2048]', 'cfg2', None,
-         lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gather)),
-        ('cfg2 per_channel_cast_and_transpose 128 [7168,2048]', 'cfg2', None, lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128)),
-        ('cfg3 swiglu_backward_and_per_token_cast g128 round_sf, input scales powers of two [16384,4096]', 'cfg3',
-         backward_inputs, lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
-        ('cfg1 moe.expand_to_fused_with_sf of the FP8 cast, 8 positions per token, ue8m0 scales [4096,7168] -> [32768,7168]', 'cfg1',
-         expand_inputs, lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True)),
+    def spec(kernel, operation, cfg, op, prepare=None, **params):
+        return {'kernel': kernel, 'operation': operation, 'cfg': cfg, 'op': op, 'prepare': prepare, 'params': params}
+
+    return [
+        spec('per_token_cast', 'cfg1', 'cfg1', lambda x: quant.per_token_cast(x, 'e4m3', 128), fmt='e4m3', group=128, sf='fp32'),
+        spec('per_token_cast', 'cfg1', 'cfg1', lambda x: quant.per_token_cast(x, 'e4m3', 128, round_sf=True), fmt='e4m3', group=128, sf='fp32 pow2'),
+        spec('per_block_cast', 'cfg2', 'cfg2', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128)), fmt='e4m3', block='128x128'),
+        spec('per_channel_cast', 'cfg2', 'cfg2', lambda x: quant.per_channel_cast(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
+        spec('swiglu_forward_and_per_token_cast', 'cfg3', 'cfg3', lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128),
+             fmt='e4m3', group=128, sf='fp32'),
+        spec('swiglu_forward_and_per_token_cast', 'cfg3', 'cfg3', lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128, **ue),
+             fmt='e4m3', group=128, sf='ue8m0'),
+        spec('per_token_cast', 'cfg4', 'cfg4', lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True), fmt='e2m1', group=32, sf='ue8m0'),
+        spec('per_token_cast', 'cfg4', 'cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1]), fmt='e5m6', group=7168, sf='fp32'),
+        # the tile kernels in steady state: 14336 tiles, 16 times the resident blocks
+        spec('per_block_cast', 'large', 'cfg4', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128)), fmt='e4m3', block='128x128'),
+        spec('per_channel_cast', 'large', 'cfg4', lambda x: quant.per_channel_cast(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
+        # the rows next to the hot path
+        spec('per_token_cast_back', 'cfg4', 'cfg4', lambda q: (quant.per_token_cast_back(q, 'bf16', 128),),
+             lambda x: quant.per_token_cast(x, 'e4m3', 128, None, **ue), fmt='e4m3', group=128, sf='ue8m0', out='bf16'),
+        spec('per_token_cast_back', 'cfg4', 'cfg4', lambda q: (quant.per_token_cast_back(q, 'bf16', 7168, x_special_fmt='e5m6'),),
+             lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1]), fmt='e5m6', out='bf16'),
+        spec('per_token_cast', 'cfg4 requantise', 'cfg4', lambda q: quant.per_token_cast(q, 'e4m3', 128, (128, 128), **ue),
+             lambda x: quant.per_block_cast(x, 'e4m3', (128, 128), **ue), fmt='e4m3', group=128, x='e4m3 128x128 ue8m0'),
+        spec('per_channel_cast_fused', 'cfg2 gather', 'cfg2', lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gathers[x.shape[0]]),
+             fmt='e4m3', rows_out=8192),
+        spec('per_channel_cast_and_transpose', 'cfg2', 'cfg2', lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
+        spec('swiglu_backward_and_per_token_cast', 'cfg3', 'cfg3', lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True),
+             backward_inputs, group=128, sf='fp32 pow2', x_sf='pow2'),
+        spec('expand_to_fused_with_sf', 'cfg1', 'cfg1', lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True), expand_inputs,
+             x='e4m3 + ue8m0', positions_per_token=8),
     ]
+
+
+def bench_other_ops(torch, quant, device, count_bytes) -> list:
+    """The per-op table on one GPU.  Working sets below the L2 size are timed L2-cold: each launch uses the next of
+    `sets` distinct input/output sets whose total size exceeds twice the L2.  Beside every op: a device copy of the
+    same number of bytes timed the same way, and the host cost of one eager call."""
+    from tilekernels_b200 import moe
+    from tilekernels_b200.testing import make_config_input
+    peak, _ = hbm_peak()
 
     def clone(v):
         return tuple(clone(t) for t in v) if isinstance(v, tuple) else v.clone()
 
-    cache, results = {}, []
-    for label, cfg, prepare, op in specs:
+    def shape_of(v):
+        while isinstance(v, tuple):
+            v = v[0]
+        return list(v.shape)
+
+    cache, copies, results = {}, {}, []
+    for s in op_specs(torch, quant, moe, device):
+        cfg, prepare, op = s['cfg'], s['prepare'], s['op']
         if cfg not in cache:
             cache.clear()
+            torch.cuda.empty_cache()
             cache[cfg] = make_config_input(cfg).to(device)
+        tiny = make_config_input(cfg, 128).to(device)
+        host_us = host_us_per_call(torch, op, tiny if prepare is None else prepare(tiny))
         x = cache[cfg] if prepare is None else prepare(cache[cfg])
         out = op(x)
         nbytes = count_bytes(x, out)
@@ -232,10 +299,18 @@ def bench_other_ops(torch, quant, device, count_bytes) -> list:
         del out
         xs = [x] + [clone(x) for _ in range(sets - 1)]
         med, best = time_graph(torch, op, xs, launches=2 * sets)
+        shape = shape_of(x)
         del xs, x
         torch.cuda.empty_cache()
-        results.append({'op': label, 'bytes': nbytes, 'us_median': round(med, 2), 'us_min': round(best, 2),
-                        'gbs': round(nbytes / med / 1e3, 1), 'frac_of_hbm_peak': round(nbytes / med / 1e3 / peak, 3),
+        if nbytes not in copies:
+            copies[nbytes] = time_copy(torch, device, nbytes)
+            torch.cuda.empty_cache()
+        params = dict(s['params'], shape=shape)
+        results.append({'kernel': s['kernel'], 'operation': s['operation'], 'params': params, 'bytes': nbytes,
+                        'time_us': round(med, 2), 'us_min': round(best, 2), 'bandwidth_gbs': round(nbytes / med / 1e3, 1),
+                        'frac_of_hbm_peak': round(nbytes / med / 1e3 / peak, 3),
+                        'copy_us': round(copies[nbytes], 2), 'frac_of_same_size_copy': round(copies[nbytes] / med, 3),
+                        'host_us_per_call': round(host_us, 1),
                         'l2': f'cold: {sets} rotating input/output sets, {2 * sets} launches per CUDA graph replay'})
     return results
 
@@ -296,14 +371,70 @@ def run_reference(args) -> None:
         'impl': 'reference', 'metric': 'per_token_cast_fp8_e4m3_g128_ue8m0_throughput', 'value': round(value, 3), 'unit': 'Mtokens/s',
         'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(dt / args.steps * 1e3, 3),
         'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': f'cfg5 per-token FP8 e4m3 cast, group 128, ue8m0 col-major scales, bf16 [{TOTAL_ROWS},{HIDDEN}]',
-                   'sample': sample},
+        'config': workload_config(TOTAL_ROWS, args.gpus),
         'hbm_gbs': round(value * bytes_per_token() / 1e3, 3),
         'cpu_baseline': {'value': round(value, 3), 'unit': 'Mtokens/s', 'cores': cores, 'kind': 'port', 'sample': sample, 'cpu': cpu_model()},
         'e2e': {'value': round(value, 3), 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def shard_parity(torch, oracle, x_host, out, sf, rows: int) -> bool:
+    """Outside every timed region: the first and the last 4096-row band of this rank's shard, cast by the oracle on
+    the host, must equal what the rank's kernel wrote (codes and scale words)."""
+    ok = True
+    band = min(4096, rows)
+    for r0 in sorted({0, rows - band}):
+        want_out, want_sf = oracle.cast(x_host[r0:r0 + band], 'e4m3', (1, GROUP), round_sf=True, use_tma_aligned_col_major_sf=True,
+                                        use_packed_ue8m0=True)
+        got_out = out[r0:r0 + band].cpu().view(torch.uint8)
+        got_sf = sf[r0:r0 + band].contiguous().cpu()
+        ok = ok and torch.equal(got_out, want_out.view(torch.uint8)) and torch.equal(got_sf, want_sf.contiguous())
+    return ok
+
+
+def copy_ceiling_ms(torch, pipe, x_host, out_host, sf_host, device, steps: int, barrier) -> dict:
+    """What the host <-> device links allow for the end-to-end call, measured two ways (all ranks at the same time):
+    `pipeline`: the same chunked copies on the same streams as HostCastPipeline, without the kernels;
+    `bulk`: one large host-to-device copy of the input and one device-to-host copy of the output, concurrently."""
+    rows = x_host.shape[0]
+    x_dev = torch.empty_like(x_host, device=device)
+    out_dev = torch.empty(out_host.shape, dtype=torch.uint8, device=device)
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def bulk():
+        cur = torch.cuda.current_stream(device)
+        up.wait_stream(cur)
+        down.wait_stream(cur)
+        with torch.cuda.stream(up):
+            x_dev.copy_(x_host, non_blocking=True)
+        with torch.cuda.stream(down):
+            out_host.view(torch.uint8).copy_(out_dev, non_blocking=True)
+        cur.wait_stream(up)
+        cur.wait_stream(down)
+
+    def pipeline():
+        cur = torch.cuda.current_stream(device)
+        pipe.h2d.wait_stream(cur)
+        pipe.d2h.wait_stream(cur)
+        for i, r0 in enumerate(range(0, rows, pipe.chunk_rows)):
+            n = min(pipe.chunk_rows, rows - r0)
+            slot = i % pipe.depth
+            with torch.cuda.stream(pipe.h2d):
+                if i >= pipe.depth:
+                    pipe.h2d.wait_event(pipe.ev_free[slot])
+                pipe.x_dev[slot][:n].copy_(x_host[r0:r0 + n], non_blocking=True)
+                pipe.ev_loaded[slot].record(pipe.h2d)
+            with torch.cuda.stream(pipe.d2h):
+                pipe.d2h.wait_event(pipe.ev_loaded[slot])
+                out_host[r0:r0 + n].view(torch.uint8).copy_(pipe.out_dev[slot][:n], non_blocking=True)
+                pipe.ev_free[slot].record(pipe.d2h)
+        cur.wait_stream(pipe.d2h)
+
+    ms_bulk, _, _ = time_steps(torch, bulk, steps, 2, barrier)
+    ms_pipe, _, _ = time_steps(torch, pipeline, steps, 2, barrier)
+    return {'bulk': ms_bulk / steps, 'pipeline': ms_pipe / steps}
 
 
 def run_ours(args) -> None:
@@ -347,21 +478,37 @@ def run_ours(args) -> None:
     if clocks['samples'] == 0:  # a timed region shorter than the sampling period: use the samples around it
         clocks = sampler.summary()
 
+    # what the ranks wrote, checked against the CPU checker on the first and last band of every shard
+    import oracle
+    out_dev, sf_dev = step()
+    parity_ok = shard_parity(torch, oracle, x_host, out_dev, sf_dev, rows)
+    del out_dev, sf_dev
+
     # end to end through the host-buffer API
     out_host = torch.empty((rows, HIDDEN), dtype=torch.float8_e4m3fn, pin_memory=True)
     sf_host = torch.empty((HIDDEN // GROUP // 4, rows), dtype=torch.int32, pin_memory=True)
-    pipe = host.HostCastPipeline(device, hidden=HIDDEN, max_rows=rows)
+    chunk_rows = max(1024, min(4096, rows // 16 // 256 * 256))  # at least 16 chunks per call keep the ring busy
+    pipe = host.HostCastPipeline(device, hidden=HIDDEN, max_rows=rows, chunk_rows=chunk_rows, depth=4)
 
     def e2e_step():
         pipe.per_token_cast_host(x_host, 'e4m3', GROUP, out_host, sf_host)
 
     e2e_steps = max(1, min(args.steps, 5))
     ms_e2e, _, _ = time_steps(torch, e2e_step, e2e_steps, 3, barrier)
+    e2e_parity = torch.equal(out_host[:chunk_rows].view(torch.uint8), step()[0][:chunk_rows].cpu().view(torch.uint8))
+    ceiling = copy_ceiling_ms(torch, pipe, x_host, out_host, sf_host, device, max(1, min(args.steps, 3)), barrier)
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=device)
+    mine = torch.tensor([ms, ms_e2e, ceiling['bulk'], ceiling['pipeline'], 1.0 if (parity_ok and e2e_parity) else 0.0],
+                        dtype=torch.float64, device=device)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        table = torch.stack(everyone).cpu()
+    else:
+        table = mine.cpu().unsqueeze(0)
+    ms, ms_e2e, ms_bulk, ms_pipe = (float(table[:, i].max()) for i in range(4))
+    parity_all = bool(table[:, 4].min() > 0.5)
+    per_rank = sorted(float(v) / args.steps for v in table[:, 0])
 
     if rank == 0:
         peak, peak_kind = hbm_peak()
@@ -369,24 +516,35 @@ def run_ours(args) -> None:
         value = total_rows / (ms_per_step * 1e-3) / 1e6
         kernel_gbs = rows * bytes_per_token() / (ms_per_step * 1e-3) / 1e9  # per GPU: one launch per step on each rank
         e2e_value = total_rows / (ms_e2e / e2e_steps * 1e-3) / 1e6
+        ceiling_value = total_rows / (max(ms_bulk, 1e-9) * 1e-3) / 1e6
+        traffic = profiled_traffic()
         line = {
             'metric': 'per_token_cast_fp8_e4m3_g128_ue8m0_throughput', 'value': round(value, 2), 'unit': 'Mtokens/s',
             'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(ms_per_step, 4),
             'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-            'config': {'workload': f'cfg5 per-token FP8 e4m3 cast, group 128, ue8m0 col-major scales, bf16 [{total_rows},{HIDDEN}]',
-                       'rows_per_rank': rows, 'sharding': f'token dimension split over {world} rank(s), no collective',
-                       'l2': 'inputs larger than L2 (no flush needed)'},
+            'config': workload_config(total_rows, world),
             'hbm_gbs': round(kernel_gbs * world, 1),
             'pct_of_8tbs': round(kernel_gbs / 8000.0 * 100, 1),
             'clocks': clocks,
+            # device time per step of every rank: the spread between ranks and the per-launch cost, separately
+            'ms_per_rank': {'min': round(per_rank[0], 4), 'median': round(statistics.median(per_rank), 4), 'max': round(per_rank[-1], 4)},
+            'shard_parity': 'ok' if parity_all else 'MISMATCH',
             # bytes of all ranks together, like `value`
             'e2e': {'value': round(e2e_value, 3), 'unit': 'Mtokens/s', 'h2d_bytes_per_step': total_rows * HIDDEN * 2,
                     'd2h_bytes_per_step': total_rows * HIDDEN + total_rows * (HIDDEN // GROUP), 'steps': e2e_steps,
-                    'api': 'tilekernels_b200.host.HostCastPipeline.per_token_cast_host (pinned host buffers)'},
+                    'api': 'tilekernels_b200.host.HostCastPipeline.per_token_cast_host (pinned host buffers)',
+                    'chunk_rows': chunk_rows, 'depth': pipe.depth,
+                    # the same bytes over the same links without any kernel, all ranks at once
+                    'copy_ceiling': {'value': round(ceiling_value, 3), 'unit': 'Mtokens/s',
+                                     'how': 'one host-to-device copy of the shard and one device-to-host copy of the output, concurrently',
+                                     'pipeline_copies_only': round(total_rows / (max(ms_pipe, 1e-9) * 1e-3) / 1e6, 3)},
+                    'frac_of_ceiling': round(e2e_value / ceiling_value, 3)},
             'gpu_launches': args.steps,
             'roofline': {'bound': 'hbm', 'achieved': round(kernel_gbs, 1), 'peak': peak, 'unit': 'GB/s',
                          'frac': round(kernel_gbs / peak, 4), 'peak_source': f'of {peak_kind}',
-                         'traffic': None if NCU_DRAM_BYTES_PER_TOKEN is None else NCU_DRAM_BYTES_PER_TOKEN * rows,
+                         'traffic': None if traffic is None else traffic['dram_bytes_per_token'] * rows,
+                         'traffic_source': None if traffic is None else
+                         f"profiler capture at commit {traffic['captured_at_commit']} ({traffic['captured_rows']} rows), scaled by rows; not measured in this run",
                          'algorithmic_bytes_per_launch': rows * bytes_per_token(), 'kernel': 'group_cast_kernel<bf16,e4m3,LPG=8>'},
         }
         if world == 1:
@@ -395,9 +553,18 @@ def run_ours(args) -> None:
             line['cpu_baseline'] = {'value': round(oracle_rate(sample_rows, cores, repeats=3), 3), 'unit': 'Mtokens/s', 'cores': cores,
                                     'kind': 'port', 'sample': f'{sample_rows} of {TOTAL_ROWS} rows, best of 3', 'cpu': cpu_model()}
             if not args.no_ops:
-                del x
+                del x, pipe
                 torch.cuda.empty_cache()
                 line['ops'] = bench_other_ops(torch, quant, device, count_bytes)
+                if args.records:
+                    # one record per op in the form of the reference's benchmark plugin (kernel, operation, params,
+                    # time_us, bandwidth_gbs, extras), one JSON object per line
+                    with open(args.records, 'w') as f:
+                        for r in line['ops']:
+                            rec = {'kernel': r['kernel'], 'operation': r['operation'], 'params': dict(sorted(r['params'].items())),
+                                   'time_us': r['time_us'], 'bandwidth_gbs': r['bandwidth_gbs'],
+                                   'extras': {'copy_us': r['copy_us'], 'host_us_per_call': r['host_us_per_call']}}
+                            f.write(json.dumps(rec) + '\n')
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -412,6 +579,7 @@ def main() -> None:
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--rows', type=int, default=0, help='total rows (default 262144); for quick runs')
     ap.add_argument('--no-ops', action='store_true', help='skip the per-op table of the other workloads')
+    ap.add_argument('--records', default='', help='also write the per-op table as JSONL records to this file')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)

@@ -1,0 +1,211 @@
+"""Out-of-bounds stores, checked without a memory checker: every output of a cast is placed inside a larger device
+buffer filled with 0xA5, the entry point is called through the raw C ABI with the interior pointer, and the WHOLE
+buffer is compared with what it must hold afterwards: the oracle's bytes at the logical positions, 0xA5 everywhere
+else -- in front of and behind the output, and in the padding of the column-major scale layouts (token padding up
+to the 16-byte pitch is never written).  Ragged shapes: tokens 1, 3, 127, 129, 4001; hidden 64 and 576."""
+import ctypes
+
+import pytest
+import torch
+
+from helpers import flags_id
+
+pytestmark = pytest.mark.gpu
+
+GUARD = 4096          # bytes in front of and behind every output
+FILL = 0xA5
+TOKENS = [1, 3, 127, 129, 4001]
+FLAG_SETS = [(False, False, False), (True, True, False), (True, True, True)]  # (col_major, round_sf, ue8m0)
+
+
+def _ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def _align(a, b):
+    return _ceil_div(a, b) * b
+
+
+class Guarded:
+    """`nbytes` of device memory surrounded by guard bytes, everything pre-filled with FILL."""
+
+    def __init__(self, nbytes: int, device):
+        self.nbytes = nbytes
+        self.buf = torch.full((GUARD + nbytes + GUARD,), FILL, dtype=torch.uint8, device=device)
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr() + GUARD
+
+    def check(self, expected_interior: torch.Tensor, what: str) -> None:
+        """expected_interior: uint8 CPU tensor of nbytes (FILL where nothing may be written)."""
+        got = self.buf.cpu()
+        want = torch.full_like(got, FILL)
+        want[GUARD:GUARD + self.nbytes] = expected_interior
+        if not torch.equal(got, want):
+            bad = torch.nonzero(got != want).flatten()
+            where = [int(b) - GUARD for b in bad[:6]]
+            raise AssertionError(f'{what}: {bad.numel()} wrong bytes, first at offsets {where} relative to the output start '
+                                 f'(logical size {self.nbytes})')
+
+
+def _sf_geometry(nm: int, nk: int, col: bool, ue: bool):
+    """(storage bytes, sf_stride argument) of the scale layouts of include/tkquant.h."""
+    if ue:
+        pitch = _align(4 * nm, 16)
+        return _ceil_div(nk, 4) * pitch, pitch
+    if col:
+        pitch = _align(nm, 4)
+        return nk * pitch * 4, pitch
+    return nm * nk * 4, nk
+
+
+def _expected_sf(sf_ref: torch.Tensor, nm: int, nk: int, col: bool, ue: bool) -> torch.Tensor:
+    """The scale storage as bytes: the oracle's values at their places, FILL in the padding."""
+    nbytes, stride = _sf_geometry(nm, nk, col, ue)
+    store = torch.full((nbytes,), FILL, dtype=torch.uint8)
+    if ue:
+        words = store.view(torch.int32).view(_ceil_div(nk, 4), stride // 4)
+        words[:, :nm] = sf_ref.T          # int32 [nm, ceil(nk / 4)], padding bytes of the last word are zero
+    elif col:
+        store.view(torch.float32).view(nk, stride)[:, :nm] = sf_ref.T
+    else:
+        store.view(torch.float32).view(nm, nk)[:] = sf_ref
+    return store
+
+
+def _flags(col, rnd, ue):
+    return (1 if rnd else 0) | (2 if col else 0) | (4 if ue else 0)
+
+
+def _raw(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous().view(torch.uint8).flatten()
+
+
+@pytest.mark.parametrize('flags', FLAG_SETS, ids=flags_id)
+@pytest.mark.parametrize('fmt,group', [('e4m3', 32), ('e4m3', 0), ('e2m1', 32)])
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_per_token_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, fmt, group, flags):
+    from tilekernels_b200 import _lib
+    col, rnd, ue = flags
+    group = group or hidden
+    if group == hidden and col:
+        pytest.skip('one scale per token is used with row-major scales')
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(num_tokens + hidden)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(x, fmt, (1, group), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+    nk = _ceil_div(hidden, group)
+    sf_bytes, sf_stride = _sf_geometry(num_tokens, nk, col, ue)
+    out = Guarded(num_tokens * (hidden if fmt == 'e4m3' else hidden // 2), cuda_device)
+    sf = Guarded(sf_bytes, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_per_token_cast(xd.data_ptr(), 0, num_tokens, hidden, hidden, 0 if fmt == 'e4m3' else 1, group,
+                                       _flags(col, rnd, ue), out.ptr, sf.ptr, sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'per_token_cast data')
+    sf.check(_expected_sf(sf_ref, num_tokens, nk, col, ue), 'per_token_cast scales')
+
+
+@pytest.mark.parametrize('flags', FLAG_SETS, ids=flags_id)
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_e5m6_guard_bands(oracle, cuda_device, num_tokens, hidden, flags):
+    from tilekernels_b200 import _lib
+    col, rnd, ue = flags
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(7 + num_tokens)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast_to_e5m6(x, hidden, col, rnd, ue)
+    sf_bytes, sf_stride = _sf_geometry(num_tokens, 1, col, ue)
+    out = Guarded(num_tokens * hidden // 8 * 12, cuda_device)
+    sf = Guarded(sf_bytes, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_per_token_cast_e5m6(xd.data_ptr(), 0, num_tokens, hidden, hidden, _flags(col, rnd, ue), out.ptr, sf.ptr,
+                                            sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'e5m6 data')
+    sf.check(_expected_sf(sf_ref, num_tokens, 1, col, ue), 'e5m6 scales')
+
+
+@pytest.mark.parametrize('flags', FLAG_SETS, ids=flags_id)
+@pytest.mark.parametrize('block', [128, 32])
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_per_block_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, block, flags):
+    from tilekernels_b200 import _lib
+    col, rnd, ue = flags
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(11 + num_tokens)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(x, 'e4m3', (block, block), round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+    nm, nk = _ceil_div(num_tokens, block), _ceil_div(hidden, block)
+    sf_bytes, sf_stride = _sf_geometry(nm, nk, col, ue)
+    out = Guarded(num_tokens * hidden, cuda_device)
+    sf = Guarded(sf_bytes, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_per_block_cast(xd.data_ptr(), 0, num_tokens, hidden, 0, block, block, _flags(col, rnd, ue), out.ptr, sf.ptr,
+                                       sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'per_block_cast data')
+    sf.check(_expected_sf(sf_ref, nm, nk, col, ue), 'per_block_cast scales')
+
+
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', [128, 384])
+def test_per_channel_cast_guard_bands(oracle, cuda_device, num_tokens, hidden):
+    from tilekernels_b200 import _lib
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(13)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(x, 'e4m3', (128, 1))
+    out = Guarded(num_tokens * hidden, cuda_device)
+    sf = Guarded(num_tokens // 128 * hidden * 4, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_per_channel_cast(xd.data_ptr(), 0, num_tokens, hidden, 0, out.ptr, sf.ptr, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'per_channel_cast data')
+    sf.check(_raw(sf_ref), 'per_channel_cast scales')
+
+
+@pytest.mark.parametrize('flags', FLAG_SETS, ids=flags_id)
+@pytest.mark.parametrize('hidden', [128, 1152])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_swiglu_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, flags):
+    """hidden 128 takes the register kernel, 1152 the staged kernel with a partly filled row segment.  Scales must be
+    exact; a data byte may differ from the oracle by one code step (approximate kernel), never in a guard byte."""
+    from tilekernels_b200 import _lib
+    col, rnd, ue = flags
+    x = torch.randn((num_tokens, 2 * hidden), generator=torch.Generator().manual_seed(17 + num_tokens)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x), 'e4m3', (1, 128), round_sf=rnd, use_tma_aligned_col_major_sf=col,
+                                  use_packed_ue8m0=ue)
+    nk = hidden // 128
+    sf_bytes, sf_stride = _sf_geometry(num_tokens, nk, col, ue)
+    out = Guarded(num_tokens * hidden, cuda_device)
+    sf = Guarded(sf_bytes, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_swiglu_forward_and_per_token_cast(xd.data_ptr(), 0, num_tokens, hidden, 128, None, None, None,
+                                                          ctypes.c_float(-1.0), None, ctypes.c_float(-1.0), 0,
+                                                          _flags(col, rnd, ue), out.ptr, sf.ptr, sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    sf.check(_expected_sf(sf_ref, num_tokens, nk, col, ue), 'swiglu cast scales')
+    got = out.buf.cpu()
+    interior = got[GUARD:GUARD + out.nbytes]
+    step = (interior.to(torch.int32) - _raw(out_ref).to(torch.int32)).abs()
+    assert int(step.max()) <= 1 and int((step > 0).sum()) <= max(1, int(1e-4 * step.numel()))
+    out.check(interior, 'swiglu cast data (guard bytes)')
+
+
+@pytest.mark.parametrize('out_dtype', [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_cast_back_guard_bands(oracle, cuda_device, num_tokens, hidden, out_dtype):
+    from tilekernels_b200 import _lib
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(19 + num_tokens)).to(torch.bfloat16)
+    q, qsf = oracle.cast(x, 'e4m3', (1, 32), round_sf=True)
+    want = oracle.cast_back((q, qsf), 'fp32', (1, 32)).to(out_dtype)
+    out = Guarded(num_tokens * hidden * (2 if out_dtype == torch.bfloat16 else 4), cuda_device)
+    qd, sd = q.to(cuda_device), qsf.to(cuda_device)
+    rc = _lib.lib().tkq_cast_back(qd.data_ptr(), 0, sd.data_ptr(), 0, hidden // 32, 1, 32, num_tokens, hidden,
+                                  0 if out_dtype == torch.bfloat16 else 1, out.ptr, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(want), 'cast_back data')

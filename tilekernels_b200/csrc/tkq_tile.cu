@@ -1,7 +1,11 @@
-// Per-block and per-channel casts: 128 x 128 tiles staged in shared memory by TMA
-// (cp.async.bulk.tensor.2d, one instruction per tile completing on an mbarrier; no
-// multicast).  Blocks are persistent and keep several tile loads in flight
-// (run_tile_pipeline).
+// Per-block and per-channel casts over 128 x 128 tiles.  Two families:
+//   * staged: tiles arrive in shared memory by TMA (cp.async.bulk.tensor.2d, one instruction per tile
+//     completing on an mbarrier; no multicast), persistent blocks keep several tile loads in flight
+//     (run_tile_pipeline) -- fp32 input, the 32-wide block shapes, the transposing casts, the
+//     per-channel cast of the largest tensors;
+//   * direct: bf16 tiles of the 128 x 128 per-block cast and of the per-channel cast are read with 256-bit
+//     loads into registers and never staged, which measured faster at every size but the largest
+//     (per_block_cast_direct_kernel, per_channel_cast_direct_kernel).
 //
 // Thread mapping inside a tile (256 threads): thread t owns the 16-column chunk
 // c16 = t % 8 of rows t / 8 + 32 * i, i = 0..3.  A warp therefore covers 4 full
@@ -252,56 +256,60 @@ __global__ void __launch_bounds__(kTileThreads) per_block_cast_kernel(const __gr
 }
 
 // ---------------------------------------------------------------------------
-// The 128 x 128 per-block and per-channel casts in their light form: ONE tile buffer per block and nothing of the
+// "Light" staging for the per-channel cast of the largest bf16 tensors: ONE tile buffer per block and nothing of the
 // tile kept in registers (the tile is read from shared memory twice, for the maximum and for the conversion), so
-// that about 40 registers suffice and six blocks (bf16) share an SM.  The blocks of an SM are in different
-// phases (waiting for their tile, reducing, converting, storing), which is what overlaps memory and arithmetic
-// here, instead of a deep ring in few fat blocks.
+// that about 40 registers suffice and six blocks share an SM.  The blocks of an SM are in different phases (waiting
+// for their tile, reducing, converting, storing), which is what overlaps memory and arithmetic here.
 // ---------------------------------------------------------------------------
 template <int DT>
 constexpr int kLightBlocksPerSm = DT == TKQ_DT_BF16 ? 6 : 3;
 
-template <int DT, int FMT>
-__global__ void __launch_bounds__(kTileThreads, kLightBlocksPerSm<DT>) per_block_cast_light_kernel(const __grid_constant__ CUtensorMap tmap,
-                                                                                                   const TileParams p) {
-    extern __shared__ __align__(128) uint8_t tile[];
-    __shared__ uint64_t bar;
-    __shared__ float warp_max[kTileThreads / 32];
+// ---------------------------------------------------------------------------
+// The 128 x 128 per-block cast of bf16 input straight from global memory: a thread loads its four 32-byte pieces of
+// the tile (rows t / 8 + 32 k, columns 16 (t % 8) ..) with 256-bit loads, keeps them packed in 32 registers for both
+// passes (maximum, conversion), and the block combines the maxima through shared memory with ONE barrier per tile
+// (the slot of the 8 warp maxima alternates between two rows).  No staging buffer, no asynchronous copy to wait
+// for: with four to five blocks per SM the loads of one block overlap the arithmetic and stores of the others.
+// ---------------------------------------------------------------------------
+template <int FMT>
+__global__ void __launch_bounds__(kTileThreads, 5) per_block_cast_direct_kernel(const TileParams p, const bool wide) {
+    __shared__ float warp_max[2][kTileThreads / 32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int c16 = t & 7, r_base = t >> 3;
     const bool round_sf = p.flags & TKQ_ROUND_SF;
     const bool cast_only = p.flags & TKQ_CAST_ONLY;
     const bool sf_only = p.flags & TKQ_SF_ONLY;
     const int64_t num_kb = (p.hidden + kTile - 1) / kTile;
-    if (t == 0) mbar_init(&bar, 1);
-    __syncthreads();
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
     uint32_t n = 0;
     for (uint32_t idx = blockIdx.x; idx < p.num_tiles; idx += gridDim.x, ++n) {
         const TileCoord c = tile_coord(p, idx);
-        if (t == 0) issue_tile<DT>(p, &tmap, idx, tile, &bar);
-        if (!mbar_wait(&bar, n & 1u)) {
-            atomicExch(&g_tile_wait_failed, 1u);
-            return;
-        }
         const bool col_ok = c16 * 16 < c.valid_cols;
+        PlainSource<TKQ_DT_BF16>::Raw raw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (col_ok && r < c.valid_rows) PlainSource<TKQ_DT_BF16>::issue(raw[k], xb + ((c.row0 + r) * p.hidden + c.col0 + c16 * 16) * 2, wide);
+            else PlainSource<TKQ_DT_BF16>::zero(raw[k]);
+        }
         float inv;
         if (cast_only) {
             inv = __fdiv_rn(1.0f, load_sf_f32_row_major(p.sf, p.sf_stride, c.tile_m, c.tile_k));
         } else {
-            float m = 0.0f;  // elements outside the tensor arrive as zeros
+            float m = 0.0f;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float v[16];
-                read_chunk<DT>(tile, r_base + 32 * k, c16, v);
+                PlainSource<TKQ_DT_BF16>::unpack(raw[k], v);
                 m = fmaxf(m, absmax16(v));
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
-            if (lane == 0) warp_max[warp] = m;
+            if (lane == 0) warp_max[n & 1][warp] = m;
             __syncthreads();
-            m = warp_max[0];
+            m = warp_max[n & 1][0];
 #pragma unroll
-            for (int w = 1; w < kTileThreads / 32; ++w) m = fmaxf(m, warp_max[w]);
+            for (int w = 1; w < kTileThreads / 32; ++w) m = fmaxf(m, warp_max[n & 1][w]);
             const Scale s = make_scale_for<FMT>(m, p.clamp_min, round_sf, p.fast_pow2);
             inv = s.inv;
             if (t == 0) {
@@ -315,15 +323,95 @@ __global__ void __launch_bounds__(kTileThreads, kLightBlocksPerSm<DT>) per_block
                 const int r = r_base + 32 * k;
                 if (r >= c.valid_rows) continue;
                 float v[16];
-                read_chunk<DT>(tile, r, c16, v);
+                PlainSource<TKQ_DT_BF16>::unpack(raw[k], v);
                 const int64_t col = c.col0 + c16 * 16;
                 if constexpr (FMT == TKQ_FMT_E4M3) quantize_store_e4m3x16(v, inv, p.out + (c.row0 + r) * p.hidden + col);
                 else quantize_store_e2m1x16(v, inv, p.out + (c.row0 + r) * (p.hidden / 2) + col / 2);
             }
         }
-        // the reads above went through the generic proxy, the next tile load goes through the async proxy
-        fence_proxy_async_smem();
+    }
+}
+
+// max of two pairs of unsigned 16-bit values; non-negative bf16 numbers order like their bit patterns
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// ---------------------------------------------------------------------------
+// The per-channel cast (128 tokens x 1 channel) of bf16 input straight from global memory, same thread mapping as the
+// direct per-block cast.  Column maxima stay packed (two |bf16| per word, compared as unsigned 16-bit integers):
+// over the thread's four rows, over the four lanes of a warp that hold the same columns (two shuffles), then over
+// the eight warps through shared memory, where thread j < 128 finishes column j, computes its scale once and
+// leaves the inverse for the conversion pass.  Two barriers per tile, nothing staged.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kTileThreads, 4) per_channel_cast_direct_kernel(const TileParams p, const bool wide) {
+    __shared__ __align__(16) uint32_t warp_colmax[kTileThreads / 32][kTile / 2];
+    __shared__ __align__(16) float col_inv[kTile];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int c16 = t & 7, r_base = t >> 3;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
+    const uint8_t* xb = static_cast<const uint8_t*>(p.x);
+    for (uint32_t idx = blockIdx.x; idx < p.num_tiles; idx += gridDim.x) {
+        const TileCoord c = tile_coord(p, idx);
+        const bool col_ok = c16 * 16 < c.valid_cols;
+        PlainSource<TKQ_DT_BF16>::Raw raw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int r = r_base + 32 * k;
+            if (col_ok && r < c.valid_rows) PlainSource<TKQ_DT_BF16>::issue(raw[k], xb + ((c.row0 + r) * p.hidden + c.col0 + c16 * 16) * 2, wide);
+            else PlainSource<TKQ_DT_BF16>::zero(raw[k]);
+        }
+        uint32_t cm[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t a = max_u16x2(raw[0].a.v[i] & 0x7FFF7FFFu, raw[1].a.v[i] & 0x7FFF7FFFu);
+            const uint32_t b = max_u16x2(raw[2].a.v[i] & 0x7FFF7FFFu, raw[3].a.v[i] & 0x7FFF7FFFu);
+            cm[i] = max_u16x2(a, b);
+            cm[i] = max_u16x2(cm[i], __shfl_xor_sync(kFullMask, cm[i], 8));
+            cm[i] = max_u16x2(cm[i], __shfl_xor_sync(kFullMask, cm[i], 16));
+        }
+        if (lane < 8) {
+            uint4* dst = reinterpret_cast<uint4*>(&warp_colmax[warp][lane * 8]);
+            dst[0] = make_uint4(cm[0], cm[1], cm[2], cm[3]);
+            dst[1] = make_uint4(cm[4], cm[5], cm[6], cm[7]);
+        }
         __syncthreads();
+        if (t < kTile) {
+            uint32_t m = warp_colmax[0][t >> 1];
+#pragma unroll
+            for (int w = 1; w < kTileThreads / 32; ++w) m = max_u16x2(m, warp_colmax[w][t >> 1]);
+            const float amax = __uint_as_float((t & 1) ? (m & 0xFFFF0000u) : (m << 16));
+            const Scale s = make_scale_for<TKQ_FMT_E4M3>(amax, p.clamp_min, round_sf, p.fast_pow2);
+            col_inv[t] = s.inv;
+            if (t < c.valid_cols) static_cast<float*>(p.sf)[c.tile_m * p.hidden + c.col0 + t] = s.sf;
+        }
+        __syncthreads();
+        if (col_ok) {
+            float inv[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 a = reinterpret_cast<const float4*>(&col_inv[c16 * 16])[q];
+                inv[4 * q] = a.x, inv[4 * q + 1] = a.y, inv[4 * q + 2] = a.z, inv[4 * q + 3] = a.w;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = r_base + 32 * k;
+                if (r >= c.valid_rows) continue;
+                float v[16], q[16];
+                PlainSource<TKQ_DT_BF16>::unpack(raw[k], v);
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float2 y = mul2(make_float2(v[j], v[j + 1]), make_float2(inv[j], inv[j + 1]));
+                    q[j] = y.x;
+                    q[j + 1] = y.y;
+                }
+                stg128(p.out + (c.row0 + r) * p.hidden + c.col0 + c16 * 16, cvt_e4m3x4(q[0], q[1], q[2], q[3]),
+                       cvt_e4m3x4(q[4], q[5], q[6], q[7]), cvt_e4m3x4(q[8], q[9], q[10], q[11]),
+                       cvt_e4m3x4(q[12], q[13], q[14], q[15]));
+            }
+        }
     }
 }
 
@@ -803,15 +891,35 @@ static int launch_tile_light(Kernel kernel, TileParams p, const char* what, cuda
     return check_launch(what);
 }
 
+// Launch of a direct tile kernel (bf16 tiles held in registers).  Resident blocks per SM were measured on B200 for
+// [7168, 2048] ... [32768, 7168]: up to 8 tiles per SM run fastest with every block resident (ramp and drain
+// dominate), mid sizes with four blocks per SM, and the largest with three (more tiles in flight than that cost
+// DRAM efficiency: 0.86 of the copy bandwidth with five blocks, 0.96 with three on [32768, 7168]).
+template <class Kernel>
+static int launch_tile_direct(Kernel kernel, TileParams p, int max_blocks_per_sm, const char* what, cudaStream_t stream) {
+    const int64_t tiles = ((p.num_tokens + kTile - 1) / kTile) * p.tiles_k;
+    if (tiles >= (int64_t{1} << 31) || p.num_tokens >= (int64_t{1} << 31))
+        return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
+    const int sms = device_sm_count();
+    int per_sm = std::min(max_blocks_per_sm, cached_occupancy(reinterpret_cast<const void*>(kernel), kTileThreads, 0));
+    if (tiles > int64_t{64} * sms) per_sm = std::min(per_sm, 3);
+    else if (tiles > int64_t{8} * sms) per_sm = std::min(per_sm, 4);
+    p.num_tiles = static_cast<uint32_t>(tiles);
+    p.stages = 0;
+    const int grid = static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sms) * per_sm));
+    kernel<<<grid, kTileThreads, 0, stream>>>(p, reinterpret_cast<uintptr_t>(p.x) % 32 == 0);
+    return check_launch(what);
+}
+
 template <int DT, int FMT>
 static int dispatch_block(const TileParams& p, int bm, int bk, cudaStream_t s) {
     constexpr int TB = TileElem<DT>::kBytes;
     const char* what = "per_block_cast";
     if (bm == 128 && bk == 128) {
-        // bf16 tiles (32 KB): the light kernel, six blocks per SM.  fp32 tiles (64 KB) fit three times only and
-        // measured faster through the ring kernel (16.9 against 23.2 us on [7168, 2048]).
-        if constexpr (DT == TKQ_DT_BF16) return launch_tile_light<DT>(per_block_cast_light_kernel<DT, FMT>, p, what, s);
-        else return launch_tile(per_block_cast_kernel<DT, FMT, 128, 128>, p, TB, what, s);
+        // bf16 tiles: the direct kernel (registers, no staging).  fp32 tiles (64 KB) go through the TMA ring kernel.
+        if constexpr (DT == TKQ_DT_BF16) {
+            return launch_tile_direct(per_block_cast_direct_kernel<FMT>, p, 5, what, s);
+        } else return launch_tile(per_block_cast_kernel<DT, FMT, 128, 128>, p, TB, what, s);
     }
     if (bm == 32 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 32, 32>, p, TB, what, s);
     if (bm == 128 && bk == 32) return launch_tile(per_block_cast_kernel<DT, FMT, 128, 32>, p, TB, what, s);
@@ -1053,6 +1161,10 @@ extern "C" int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tok
     p.clamp_min = 1e-4f;
     p.fast_pow2 = (flags & TKQ_ROUND_SF) != 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // bf16: the direct kernel, except for the largest shapes, where the staged light kernel (six blocks per SM)
+    // measured a little faster (118 against 121 us on [32768, 7168]; 11.6 against 10.4 us on [7168, 2048])
+    if (in_dtype == TKQ_DT_BF16 && (num_tokens / kTile) * p.tiles_k <= int64_t{64} * device_sm_count())
+        return launch_tile_direct(per_channel_cast_direct_kernel, p, 4, "per_channel_cast", s);
     return in_dtype == TKQ_DT_BF16
                ? launch_tile_light<TKQ_DT_BF16>(per_channel_cast_light_kernel<TKQ_DT_BF16>, p, "per_channel_cast", s)
                : launch_tile(per_channel_cast_kernel<TKQ_DT_FP32>, p, 4, "per_channel_cast", s);
