@@ -138,6 +138,7 @@ extern "C" int tkq_cast_back(const void* x, int in_fmt, const void* x_sf, unsign
     p.in_sf_flags = x_sf_flags;
     p.in_block_m = static_cast<uint32_t>(x_block_m);
     p.in_block_k = static_cast<uint32_t>(x_block_k);
+    set_input_block_shifts(p);
     p.wide_loads = reinterpret_cast<uintptr_t>(out) % 32 == 0;  // here: 256-bit *stores* are legal
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (in_fmt == TKQ_FMT_E4M3) return launch_cast_back<QuantSource<TKQ_FMT_E4M3>>(p, out_dtype, s);

@@ -270,6 +270,7 @@ extern "C" int tkq_per_token_cast_quantized(const void* x, int in_fmt, const voi
     p.in_sf_flags = x_sf_flags;
     p.in_block_m = static_cast<uint32_t>(x_block_m);
     p.in_block_k = static_cast<uint32_t>(x_block_k);
+    set_input_block_shifts(p);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (in_fmt == TKQ_FMT_E4M3)
         return fmt == TKQ_FMT_E4M3 ? dispatch_quant_group<TKQ_FMT_E4M3, TKQ_FMT_E4M3>(p, num_per_channels, s)

@@ -1,8 +1,8 @@
 // Fused SwiGLU + per-token e4m3 cast (scale groups of 128), bf16 input, rows staged by the bulk-copy engine.
 //
-// Work item: one row segment of up to 2048 activations; a block is 64 threads and every thread owns two chunks of
-// 16 activations of it (chunk t and chunk t + 64), so the per-item bookkeeping is paid once per 32 activations.
-// Thread 0 keeps `stages` items in flight, each as two cp.async.bulk copies (the gate columns and the up columns
+// Work item: one row segment of up to 2048 activations; a block is 64 threads and every thread owns 32 activations
+// of it, all in one scale group (4 lanes per group), so the per-item bookkeeping, the group reduction, the exact
+// evaluation and the scale are paid once per 32 activations.  Thread 0 keeps `stages` items in flight, each as two cp.async.bulk copies (the gate columns and the up columns
 // of the segment) into a ring of shared-memory stages that complete on one mbarrier per stage; all threads then
 // compute from shared memory and write codes and scales straight to global memory.  Bytes in flight therefore do
 // not depend on registers or on the number of resident warps.
@@ -14,13 +14,15 @@
 //   * every activation is evaluated once with ex2.approx / rcp.approx (relative error below 2^-18 for gates
 //     >= -80): these values become the FP8 codes, so a code can differ from the exactly evaluated one only when
 //     the scaled activation lies within that error of a rounding boundary;
-//   * the group maximum, which fixes the scale, is evaluated EXACTLY: every half chunk (8 values of one lane)
-//     whose approximate values come within 2^-15 of the group's approximate maximum is "flagged" (normally one
-//     per group: the one that holds the maximum); the 8 (gate, up) pairs of a flagged half chunk are evaluated
-//     again by the 8 lanes of the group, one pair each, with the exact routine -- as the two halves of one packed
-//     evaluation that serves the lane's first and second chunk at once -- and the group maximum is taken over
-//     those exact values.  The margin is 8 times the error bound, so the exactly largest element is always among
-//     the re-evaluated ones and the scale equals the scale of a fully exact evaluation bit for bit;
+//   * the group maximum, which fixes the scale, is evaluated EXACTLY: every piece (8 values of one lane) whose
+//     approximate values come within 2^-15 of the group's approximate maximum is "flagged" (normally one per
+//     group: the one that holds the maximum); the 8 (gate, up) pairs of a flagged piece are evaluated again by the
+//     4 lanes of the group, two pairs each as one packed evaluation, with the exact routine, and the group
+//     maximum is taken over those exact values.  The margin is 8 times the error bound, so the exactly largest
+//     element is always among the re-evaluated ones and the scale equals the scale of a fully exact evaluation
+//     bit for bit;
+//   * with power-of-two scales the exact evaluation is skipped whenever both ends of the interval that must hold
+//     the exact maximum give the same exponent (almost always);
 //   * a lane that holds a gate below -80 (where ex2 overflows and the error bound is lost) sends its warp's
 //     whole step through the exact routine.
 #pragma once
@@ -31,8 +33,7 @@
 namespace tkq {
 
 constexpr int kSwThreads = 64;
-constexpr int kSwChunks = 2;                              // chunks of 16 activations per thread and item
-constexpr int kSwSegment = kSwThreads * kSwChunks * 16;  // activations per work item
+constexpr int kSwSegment = kSwThreads * 32;              // activations per work item: 32 per thread
 constexpr int kSwHalfBytes = kSwSegment * 2;             // bytes of the gate (or up) part of a stage
 constexpr int kSwStageBytes = 2 * kSwHalfBytes;
 constexpr int kSwMaxStages = 4;
@@ -78,12 +79,11 @@ __device__ __noinline__ float swiglu_exact_element(float g, float u, float clamp
     return w != 1.0f ? __fmul_rn(v, w) : v;
 }
 
-// Maximum over the 8 lanes of a scale group.  (redux.sync with a sub-warp member mask was measured: it is emulated
-// and costs far more than these three shuffle + max steps.)
-__device__ __forceinline__ float group8_max(float m) {
+// Maximum over the 4 lanes of a scale group.  (redux.sync with a sub-warp member mask was measured: it is emulated
+// and costs far more than shuffle + max steps.)
+__device__ __forceinline__ float group4_max(float m) {
     m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 2));
-    return fmaxf(m, __shfl_xor_sync(kFullMask, m, 4));
+    return fmaxf(m, __shfl_xor_sync(kFullMask, m, 2));
 }
 
 // fp32 scale and inverse of the e4m3 cast without the two IEEE divisions, same bits:
@@ -105,25 +105,16 @@ __device__ __forceinline__ Scale make_scale_e4m3_nodiv(float amax, float clamp_m
     return s;
 }
 
-// 16 activations of one chunk, approximately: y = g * (r * u) with r = rcp(1 + ex2(-g * log2 e)), times the row
-// weight.  Returns the largest magnitudes of y[0..7] and y[8..15] and lowers g_min to the smallest gate.
+// 8 activations (one 16-byte piece of the gate columns and of the up columns), approximately:
+// y = g * (r * u) with r = rcp(1 + ex2(-g * log2 e)), times the row weight.  Returns the largest magnitude and
+// lowers g_min to the smallest gate.
 template <int kClampMode>
-__device__ __forceinline__ void swiglu_approx_chunk(const uint8_t* st, uint32_t chunk, bool active, float clamp, float w,
-                                                    ClampCounters& cnt, float* y, float& max_lo, float& max_hi, float& g_min) {
-    uint32_t G[8], U[8];
-    if (active) {
-        const uint4* gp = reinterpret_cast<const uint4*>(st + chunk * 32);
-        const uint4* up = reinterpret_cast<const uint4*>(st + kSwHalfBytes + chunk * 32);
-        const uint4 g0 = gp[0], g1 = gp[1], u0 = up[0], u1 = up[1];
-        G[0] = g0.x, G[1] = g0.y, G[2] = g0.z, G[3] = g0.w, G[4] = g1.x, G[5] = g1.y, G[6] = g1.z, G[7] = g1.w;
-        U[0] = u0.x, U[1] = u0.y, U[2] = u0.z, U[3] = u0.w, U[4] = u1.x, U[5] = u1.y, U[6] = u1.z, U[7] = u1.w;
-    } else {
+__device__ __forceinline__ float swiglu_approx_octet(const uint4 gw, const uint4 uw, float clamp, float w, ClampCounters& cnt,
+                                                     float* y, float& g_min) {
+    const uint32_t G[4] = {gw.x, gw.y, gw.z, gw.w}, U[4] = {uw.x, uw.y, uw.z, uw.w};
+    float g[8], u[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) G[i] = U[i] = 0;
-    }
-    float g[16], u[16];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         g[2 * i] = bf16_lo(G[i]);
         g[2 * i + 1] = bf16_hi(G[i]);
         u[2 * i] = bf16_lo(U[i]);
@@ -132,13 +123,13 @@ __device__ __forceinline__ void swiglu_approx_chunk(const uint8_t* st, uint32_t 
     if (kClampMode > 0) {
         float g_hi = 0.0f, u_hi = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
+        for (int i = 0; i < 8; i += 2) {
             g_hi = max3(g_hi, g[i], g[i + 1]);
             u_hi = max3_abs(u_hi, u[i], u[i + 1]);
         }
         if (g_hi > clamp || u_hi > clamp) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 if (kClampMode > 1) {
                     cnt.gate_hi += g[i] > clamp;
                     cnt.up_hi += u[i] > clamp;
@@ -150,15 +141,10 @@ __device__ __forceinline__ void swiglu_approx_chunk(const uint8_t* st, uint32_t 
             }
         }
     }
-    float g_min_b = 0.0f;  // two chains of four: less waiting on the previous result
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) g_min = min3(g_min, g[i], g[i + 1]);
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
-        g_min = min3(g_min, g[i], g[i + 1]);
-        g_min_b = min3(g_min_b, g[8 + i], g[8 + i + 1]);
-    }
-    g_min = fminf(g_min, g_min_b);
-#pragma unroll
-    for (int i = 0; i < 16; i += 2) {
         const float2 g2 = make_float2(g[i], g[i + 1]);
         const float2 e2 = mul2(g2, splat2(-1.4426950408889634f));
         const float2 d2 = add2(make_float2(ex2_approx(e2.x), ex2_approx(e2.y)), splat2(1.0f));
@@ -170,27 +156,47 @@ __device__ __forceinline__ void swiglu_approx_chunk(const uint8_t* st, uint32_t 
     }
     if (w != 1.0f) {  // uniform over the row
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
+        for (int i = 0; i < 8; i += 2) {
             const float2 v2 = mul2(make_float2(y[i], y[i + 1]), splat2(w));
             y[i] = v2.x;
             y[i + 1] = v2.y;
         }
     }
-    max_lo = max_hi = 0.0f;
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) m = max3_abs(m, y[i], y[i + 1]);
+    return m;
+}
+
+// 8 values, scaled -> 8 e4m3 bytes in two words
+__device__ __forceinline__ void quantize_e4m3x8(const float* v, float inv, uint32_t& w0, uint32_t& w1) {
+    float s[8];
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
-        max_lo = max3_abs(max_lo, y[i], y[i + 1]);
-        max_hi = max3_abs(max_hi, y[8 + i], y[8 + i + 1]);
+        const float2 t = mul2(make_float2(v[i], v[i + 1]), splat2(inv));
+        s[i] = t.x;
+        s[i + 1] = t.y;
     }
+    w0 = cvt_e4m3x4(s[0], s[1], s[2], s[3]);
+    w1 = cvt_e4m3x4(s[4], s[5], s[6], s[7]);
 }
 
 // kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count
+//
+// Thread mapping.  A warp covers 1024 consecutive activations of the item; the 4 lanes 4g .. 4g + 3 share scale
+// group g of those (128 activations = 16 pieces of 8).  Lane i of a group owns the pieces 2i, 2i + 1 and 8 + 2i,
+// 8 + 2i + 1: two runs of 16 consecutive activations, so that its codes leave as two 16-byte stores.  Its k-th load
+// reads piece 8 (k / 2) + 2i + ((k % 2) xor (g % 2)): even and odd groups take the two pieces of a run in opposite
+// order, and one load instruction of the warp touches every shared-memory bank exactly once.  32 activations per
+// lane and item share ONE group reduction, ONE exact evaluation (the flagged piece: 8 pairs = 4 lanes x 2), one
+// scale.
 template <int kClampMode>
 __global__ void __launch_bounds__(kSwThreads, 12)
 swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const uint32_t stages) {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full_bar[kSwMaxStages];
-    const uint32_t t = threadIdx.x, lane = t & 31;
+    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t grp = lane >> 2, sub = lane & 3, parity = grp & 1;
     const uint32_t hidden = static_cast<uint32_t>(p.hidden);
     const uint32_t total = p.total_items;
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
@@ -203,8 +209,11 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
     const float clamp_min = p.clamp_min;
     // values below half the clamp of the maximum cannot decide a scale: no exact evaluation for them
     const float thr_floor = __fmul_rn(clamp_min, 0.5f);
-    // fp32 scales: element strides of the token and the group index
-    const int64_t sf_token_stride = col_major ? 1 : p.sf_stride, sf_group_stride = col_major ? p.sf_stride : 1;
+    // first activation of the lane's group inside the item, and the byte offset of its first piece in a stage half
+    const uint32_t group_col = warp * 1024 + grp * 128;
+    const uint32_t piece0 = group_col * 2 + sub * 32;
+    // byte offsets (inside a stage half) of the pieces the lane's four loads read
+    const uint32_t off_a = piece0 + parity * 16, off_b = piece0 + (parity ^ 1u) * 16;
     ClampCounters cnt;
 
     if (t == 0) {
@@ -214,6 +223,7 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
 
     // producer (thread 0): the next item to look at and the number of loads issued so far
     uint32_t p_item = blockIdx.x, p_loads = 0, p_stage = 0;
+    const uint64_t policy = l2_evict_first_policy();  // the input is read once
     auto produce = [&](uint32_t limit) {
         while (p_loads < limit && p_item < total) {
             const uint32_t row = nseg == 1 ? p_item : p_item / nseg, seg = p_item - row * nseg;
@@ -223,8 +233,8 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
                 uint8_t* dst = ring + static_cast<size_t>(p_stage) * kSwStageBytes;
                 const uint8_t* src = xb + (static_cast<int64_t>(row) * p.x_stride + col0) * 2;
                 mbar_arrive_expect_tx(full_bar + p_stage, 2 * bytes);
-                bulk_load(dst, src, bytes, full_bar + p_stage);
-                bulk_load(dst + kSwHalfBytes, src + static_cast<int64_t>(hidden) * 2, bytes, full_bar + p_stage);
+                bulk_load_hint(dst, src, bytes, full_bar + p_stage, policy);
+                bulk_load_hint(dst + kSwHalfBytes, src + static_cast<int64_t>(hidden) * 2, bytes, full_bar + p_stage, policy);
                 ++p_loads;
                 p_stage = p_stage + 1 == stages ? 0 : p_stage + 1;
             }
@@ -260,117 +270,113 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
 
         const uint32_t seg_col = seg * kSwSegment;
         const uint32_t width = min(static_cast<uint32_t>(kSwSegment), hidden - seg_col);  // a multiple of 128
-        if ((t & ~31u) * 16 >= width) continue;  // warp-uniform: even this warp's first chunks lie beyond the row
+        if (warp * 1024 >= width) continue;     // warp-uniform: this warp's columns lie beyond the row
+        const bool active = group_col < width;  // whole groups (4 lanes) are active or not
         float w = 1.0f;
         if (p.pos_to_token_topk != nullptr) {
             const int32_t pos = p.pos_to_token_topk[row];
             w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
         }
 
-        // --- approximate evaluation of the thread's two chunks (whole groups of 8 lanes are active or not) ---
-        float y[kSwChunks][16], max_lo[kSwChunks], max_hi[kSwChunks];
-        bool active[kSwChunks];
+        // --- approximate evaluation of the lane's four pieces ---
+        float y[4][8], piece_max[4];
         float g_min = 0.0f;
 #pragma unroll
-        for (int c = 0; c < kSwChunks; ++c) {
-            const uint32_t chunk = t + c * kSwThreads;
-            active[c] = chunk * 16 < width;
-            swiglu_approx_chunk<kClampMode>(st, chunk, active[c], clamp, w, cnt, y[c], max_lo[c], max_hi[c], g_min);
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t off = ((k & 1) ? off_b : off_a) + (k >> 1) * 128;
+            uint4 gw = make_uint4(0, 0, 0, 0), uw = make_uint4(0, 0, 0, 0);
+            if (active) {
+                gw = *reinterpret_cast<const uint4*>(st + off);
+                uw = *reinterpret_cast<const uint4*>(st + kSwHalfBytes + off);
+            }
+            piece_max[k] = swiglu_approx_octet<kClampMode>(gw, uw, clamp, w, cnt, y[k], g_min);
         }
 
-        float amax[kSwChunks];
+        float amax;
         if (__any_sync(kFullMask, g_min < -80.0f)) {
-            // rare: both chunks through the exact routine (the stage still holds the inputs)
+            // rare: the whole step through the exact routine (the stage still holds the inputs)
+            float m = 0.0f;
 #pragma unroll
-            for (int c = 0; c < kSwChunks; ++c) {
-                const uint32_t chunk = t + c * kSwThreads;
-                const uint16_t* gs = reinterpret_cast<const uint16_t*>(st + chunk * 32);
-                const uint16_t* us = reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + chunk * 32);
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t off = ((k & 1) ? off_b : off_a) + (k >> 1) * 128;
+                const uint16_t* gs = reinterpret_cast<const uint16_t*>(st + off);
+                const uint16_t* us = reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + off);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float gi = active[c] ? __uint_as_float(static_cast<uint32_t>(gs[i]) << 16) : 0.0f;
-                    const float ui = active[c] ? __uint_as_float(static_cast<uint32_t>(us[i]) << 16) : 0.0f;
-                    y[c][i] = swiglu_exact_element(gi, ui, kClampMode > 0 ? clamp : -1.0f, w);
+                for (int i = 0; i < 8; ++i) {
+                    const float gi = active ? __uint_as_float(static_cast<uint32_t>(gs[i]) << 16) : 0.0f;
+                    const float ui = active ? __uint_as_float(static_cast<uint32_t>(us[i]) << 16) : 0.0f;
+                    y[k][i] = swiglu_exact_element(gi, ui, kClampMode > 0 ? clamp : -1.0f, w);
+                    m = fmaxf(m, fabsf(y[k][i]));
                 }
-                amax[c] = group8_max(absmax16(y[c]));
             }
+            amax = group4_max(m);
         } else {
-            float approx_max[kSwChunks];
-            bool undecided = !fast_pow2;
-#pragma unroll
-            for (int c = 0; c < kSwChunks; ++c) {
-                approx_max[c] = group8_max(fmaxf(max_lo[c], max_hi[c]));
-                if (fast_pow2) {
-                    // a power-of-two scale only depends on the binade of the maximum and on whether its mantissa exceeds
-                    // 1.75: when both ends of the interval that must contain the exact maximum give the same exponent,
-                    // the scale is decided without any exact evaluation
-                    const float lo_end = fmaxf(__fmaf_rn(approx_max[c], -3.0517578125e-05f, approx_max[c]), clamp_min);
-                    const float hi_end = fmaxf(__fmaf_rn(approx_max[c], 3.0517578125e-05f, approx_max[c]), clamp_min);
-                    constexpr uint32_t kCarry = FmtTraits<TKQ_FMT_E4M3>::kMantCarry;
-                    undecided = undecided || ((__float_as_uint(lo_end) + kCarry) >> 23) != ((__float_as_uint(hi_end) + kCarry) >> 23);
-                }
+            const float approx_max = group4_max(fmaxf(max3(piece_max[0], piece_max[1], piece_max[2]), piece_max[3]));
+            bool undecided = true;
+            if (fast_pow2) {
+                // a power-of-two scale only depends on the binade of the maximum and on whether its mantissa exceeds
+                // 1.75: when both ends of the interval that must contain the exact maximum give the same exponent,
+                // the scale is decided without any exact evaluation
+                const float lo_end = fmaxf(__fmaf_rn(approx_max, -3.0517578125e-05f, approx_max), clamp_min);
+                const float hi_end = fmaxf(__fmaf_rn(approx_max, 3.0517578125e-05f, approx_max), clamp_min);
+                constexpr uint32_t kCarry = FmtTraits<TKQ_FMT_E4M3>::kMantCarry;
+                undecided = ((__float_as_uint(lo_end) + kCarry) >> 23) != ((__float_as_uint(hi_end) + kCarry) >> 23);
             }
             if (!__any_sync(kFullMask, undecided)) {
-#pragma unroll
-                for (int c = 0; c < kSwChunks; ++c) amax[c] = approx_max[c];
+                amax = approx_max;
             } else {
-            // --- which half chunks can hold the exact maximum of their group: bit l = first half of lane l of the
-            //     group, bit 8 + l = its second half ---
-            uint32_t todo[kSwChunks];
+                // --- which pieces can hold the exact maximum of their group: bit 4k + i = the k-th piece of lane i ---
+                const float thr = fmaxf(__fmaf_rn(approx_max, -3.0517578125e-05f, approx_max), thr_floor);
+                uint32_t todo = 0;
 #pragma unroll
-            for (int c = 0; c < kSwChunks; ++c) {
-                const float thr = fmaxf(__fmaf_rn(approx_max[c], -3.0517578125e-05f, approx_max[c]), thr_floor);
-                const uint32_t lo = __ballot_sync(kFullMask, max_lo[c] >= thr), hi = __ballot_sync(kFullMask, max_hi[c] >= thr);
-                todo[c] = ((lo >> (lane & 24u)) & 0xFFu) | (((hi >> (lane & 24u)) & 0xFFu) << 8);
-            }
-            // --- their 8 pairs again, exactly: one pair per lane of the group, first chunk in .x, second in .y ---
-            float exact_max[kSwChunks] = {0.0f, 0.0f};
-            while (true) {
-                float gx[kSwChunks], ux[kSwChunks];
-#pragma unroll
-                for (int c = 0; c < kSwChunks; ++c) {
-                    gx[c] = 1.0f, ux[c] = 0.0f;  // nothing flagged: a pair whose activation is 0
-                    if (todo[c] != 0) {
-                        const uint32_t h = __ffs(todo[c]) - 1;
-                        const uint32_t off = ((t & ~7u) + (h & 7u) + c * kSwThreads) * 32 + (h >> 3) * 16 + (lane & 7u) * 2;
-                        gx[c] = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(st + off)) << 16);
-                        ux[c] = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(st + kSwHalfBytes + off)) << 16);
-                        todo[c] &= todo[c] - 1;
+                for (int k = 0; k < 4; ++k)
+                    todo |= ((__ballot_sync(kFullMask, piece_max[k] >= thr) >> (lane & 28u)) & 0xFu) << (4 * k);
+                // --- their 8 pairs again, exactly: two pairs per lane of the group ---
+                float exact_max = 0.0f;
+                while (true) {
+                    if (todo != 0) {
+                        const uint32_t h = __ffs(todo) - 1;
+                        // bit h = 4k + i: the k-th piece of lane i of the group
+                        const uint32_t off = group_col * 2 + (h >> 3) * 128 + (h & 3u) * 32 + ((((h >> 2) & 1u) ^ parity) << 4) + sub * 4;
+                        const uint32_t gw = *reinterpret_cast<const uint32_t*>(st + off);
+                        const uint32_t uw = *reinterpret_cast<const uint32_t*>(st + kSwHalfBytes + off);
+                        float2 g2 = make_float2(bf16_lo(gw), bf16_hi(gw));
+                        float2 u2 = make_float2(bf16_lo(uw), bf16_hi(uw));
+                        if (kClampMode > 0) {
+                            g2.x = g2.x > clamp ? clamp : g2.x;
+                            g2.y = g2.y > clamp ? clamp : g2.y;
+                            u2.x = fminf(fmaxf(u2.x, -clamp), clamp);
+                            u2.y = fminf(fmaxf(u2.y, -clamp), clamp);
+                        }
+                        float2 f2 = swiglu_exact2(g2, u2, bf16_gates);
+                        if (w != 1.0f) f2 = mul2(f2, splat2(w));
+                        exact_max = max3_abs(exact_max, f2.x, f2.y);
+                        todo &= todo - 1;
                     }
+                    if (!__any_sync(kFullMask, todo != 0)) break;
                 }
-                float2 g2 = make_float2(gx[0], gx[1]), u2 = make_float2(ux[0], ux[1]);
-                if (kClampMode > 0) {
-                    g2.x = g2.x > clamp ? clamp : g2.x;
-                    g2.y = g2.y > clamp ? clamp : g2.y;
-                    u2.x = fminf(fmaxf(u2.x, -clamp), clamp);
-                    u2.y = fminf(fmaxf(u2.y, -clamp), clamp);
-                }
-                float2 f2 = swiglu_exact2(g2, u2, bf16_gates);
-                if (w != 1.0f) f2 = mul2(f2, splat2(w));
-                exact_max[0] = fmaxf(exact_max[0], fabsf(f2.x));
-                exact_max[1] = fmaxf(exact_max[1], fabsf(f2.y));
-                if (!__any_sync(kFullMask, (todo[0] | todo[1]) != 0)) break;
-            }
-#pragma unroll
-            for (int c = 0; c < kSwChunks; ++c) amax[c] = group8_max(exact_max[c]);
+                amax = group4_max(exact_max);
             }
         }
 
-        uint8_t* out_row = p.out + static_cast<int64_t>(row) * p.out_stride + seg_col;
+        Scale sc;
+        if (fast_pow2) sc = make_scale_pow2<TKQ_FMT_E4M3>(amax, clamp_min);
+        else if (!round_sf && amax <= 1.2676506e30f) sc = make_scale_e4m3_nodiv(amax, clamp_min);
+        else sc = make_scale(amax, clamp_min, 448.0f, round_sf);
+        if (active) {
+            if (sub == 0) {
+                const uint32_t group_index = (seg_col + group_col) >> 7;
+                if (ue8m0) store_sf_ue8m0_byte(p.sf, p.sf_stride, row, group_index, p.num_groups, sc.e8);
+                else store_sf_f32(p.sf, p.sf_stride, col_major, row, group_index, sc.sf);
+            }
+            uint8_t* out_run0 = p.out + static_cast<int64_t>(row) * p.out_stride + seg_col + group_col + sub * 16;
 #pragma unroll
-        for (int c = 0; c < kSwChunks; ++c) {
-            const uint32_t chunk = t + c * kSwThreads;
-            Scale sc;
-            if (fast_pow2) sc = make_scale_pow2<TKQ_FMT_E4M3>(amax[c], clamp_min);
-            else if (!round_sf && amax[c] <= 1.2676506e30f) sc = make_scale_e4m3_nodiv(amax[c], clamp_min);
-            else sc = make_scale(amax[c], clamp_min, 448.0f, round_sf);
-            if (active[c]) {
-                if ((lane & 7u) == 0) {
-                    const uint32_t grp = (seg_col + chunk * 16) >> 7;
-                    if (ue8m0) store_sf_ue8m0_byte(p.sf, p.sf_stride, row, grp, p.num_groups, sc.e8);
-                    else static_cast<float*>(p.sf)[row * sf_token_stride + grp * sf_group_stride] = sc.sf;
-                }
-                quantize_store_e4m3x16(y[c], sc.inv, out_row + chunk * 16);
+            for (int run = 0; run < 2; ++run) {
+                uint32_t a0, a1, b0, b1;
+                quantize_e4m3x8(y[2 * run], sc.inv, a0, a1);
+                quantize_e4m3x8(y[2 * run + 1], sc.inv, b0, b1);
+                // odd groups hold the two pieces of a run in swapped order
+                stg128(out_run0 + run * 64, parity ? b0 : a0, parity ? b1 : a1, parity ? a0 : b0, parity ? a1 : b1);
             }
         }
     }

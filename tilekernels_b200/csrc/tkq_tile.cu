@@ -1307,6 +1307,7 @@ extern "C" int tkq_per_block_cast_lossless(const void* x, const void* x_sf, unsi
     p.in.in_sf_flags = x_sf_flags;
     p.in.in_block_m = static_cast<uint32_t>(x_block_m);
     p.in.in_block_k = static_cast<uint32_t>(x_block_k);
+    set_input_block_shifts(p.in);
     p.sf = sf;
     p.sf_stride = sf_stride;
     p.out_bm = static_cast<uint32_t>(out_block_m);

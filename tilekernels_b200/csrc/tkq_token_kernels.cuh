@@ -48,14 +48,28 @@ struct TokenCastParams {
     int64_t in_sf_stride;
     uint32_t in_sf_flags;  // TKQ_SF_COL_MAJOR, TKQ_SF_UE8M0
     uint32_t in_block_m, in_block_k;
+    uint32_t in_shift_m1, in_shift_k1;  // 1 + log2 of the block sizes when they are powers of two, else 0 (divide)
 };
+
+// Fills in_shift_*1 from in_block_*.
+inline void set_input_block_shifts(TokenCastParams& p) {
+    auto shift1 = [](uint32_t v) -> uint32_t {
+        if (v == 0 || (v & (v - 1)) != 0) return 0;
+        uint32_t s = 0;
+        while ((1u << s) < v) ++s;
+        return s + 1;
+    };
+    p.in_shift_m1 = shift1(p.in_block_m);
+    p.in_shift_k1 = shift1(p.in_block_k);
+}
 
 constexpr int kSourcePlain = 0, kSourceSwiglu = 1, kSourceQuant = 2;
 
 // The input scale that applies to (row, col) of an already quantized input
 // (reference: tile_kernels/quant/common.py:219-235 load_sf + transform_sf).
 __device__ __forceinline__ float load_input_scale(const TokenCastParams& p, uint32_t row, uint32_t col) {
-    const int64_t m = row / p.in_block_m, k = col / p.in_block_k;
+    const int64_t m = p.in_shift_m1 ? row >> (p.in_shift_m1 - 1) : row / p.in_block_m;
+    const int64_t k = p.in_shift_k1 ? col >> (p.in_shift_k1 - 1) : col / p.in_block_k;
     if (p.in_sf_flags & TKQ_SF_UE8M0) {
         const uint8_t e = static_cast<const uint8_t*>(p.in_sf)[(k >> 2) * p.in_sf_stride + 4 * m + (k & 3)];
         return __uint_as_float(static_cast<uint32_t>(e) << 23);

@@ -6,7 +6,8 @@
 ops: cfg1 (per-token e4m3, fp32 scales), cfg2_block, cfg2_channel, cfg3 (SwiGLU + cast), cfg4_fp4, cfg4_e5m6,
 cfg5 (per-token e4m3, ue8m0 scales), back_e4m3 / back_e5m6 (dequantisation of cfg4's tensor to bf16), bwd (SwiGLU
 backward + cast on cfg3's tensor quantised with power-of-two scales), expand (row expansion of cfg1's FP8 cast with
-ue8m0 scales to 8 positions per token).  --rows limits the row count (same per-row distribution).
+ue8m0 scales to 8 positions per token), requant (per-token e4m3 cast of cfg4's tensor already quantised per 128x128 block
+with ue8m0 scales), large_block / large_channel (the tile casts on cfg4's [32768, 7168] tensor).  --rows limits the row count (same per-row distribution).
 """
 import argparse
 
@@ -27,6 +28,9 @@ OPS = {
     'bwd': ('cfg3', lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True)),
     'expand': ('cfg1', lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True)),
     'cfg5': ('cfg5', lambda x: quant.per_token_cast(x, 'e4m3', 128, None, True, True, True)),
+    'requant': ('cfg4', lambda q: quant.per_token_cast(q, 'e4m3', 128, (128, 128), True, True, True)),
+    'large_block': ('cfg4', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128))),
+    'large_channel': ('cfg4', lambda x: quant.per_channel_cast(x, 'e4m3', 128)),
 }
 
 
@@ -40,6 +44,8 @@ def main() -> None:
     x = make_config_input(cfg, args.rows).cuda()
     if args.op == 'back_e4m3':
         x = quant.per_token_cast(x, 'e4m3', 128)
+    elif args.op == 'requant':
+        x = quant.per_block_cast(x, 'e4m3', (128, 128), True, True, True)
     elif args.op == 'back_e5m6':
         x = quant.per_token_cast(x, 'e5m6', x.shape[1])
     elif args.op == 'bwd':
