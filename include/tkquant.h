@@ -254,9 +254,17 @@ int tkq_per_channel_cast_and_transpose(const void* x, int64_t num_tokens, int64_
  *   clamped_count      optional int64[3], atomically incremented by the numbers of
  *                      gate > c, up > c, up < -c (needs swiglu_clamp >= 0)
  *   sf_clamp_min       < 0: the format default 1e-4; else the lower clamp of the group maximum
- *   num_sms            > 0 limits the grid of the counting variant to num_sms * 4 blocks
+ *   num_sms            > 0 limits the grid of the counting variant to the blocks that fit num_sms SMs
  *                      (tile_kernels/config.py:13-23); 0 = all SMs
  *   out                [num_tokens, hidden] bytes
+ *
+ * Arithmetic.  Scales (and clamp counters) are those of an evaluation of y with IEEE operations and a
+ * reproducible exp (the routine the CPU checker shares), bit for bit, whatever kernel serves the call.  The FP8
+ * codes: for bf16 input, groups of 128, hidden >= 1024 and sf_clamp_min >= 1e-30 the library uses a kernel that
+ * evaluates y with the hardware's approximate exp2 and reciprocal (exact only around each group's maximum); a code
+ * then differs from the exactly evaluated one only where the scaled activation lies within about 2^-18 of a rounding
+ * boundary -- about one code in a million, by one step.  TKQ_EXACT_CODES in `flags` selects the exact evaluation of
+ * every activation (at about two thirds of the speed); every other shape takes it anyway.
  */
 int tkq_swiglu_forward_and_per_token_cast(const void* x, int in_dtype, int64_t num_tokens, int64_t hidden,
                                           int64_t num_per_channels, const int32_t* pos_to_token_topk,

@@ -90,6 +90,6 @@ int ensure_dynamic_smem(const void* kernel, int bytes) {
 
 }  // namespace tkq
 
-extern "C" int tkq_version(void) { return 100; }
+extern "C" int tkq_version(void) { return 200; }
 
 extern "C" const char* tkq_last_error_string(void) { return tkq::g_error; }

@@ -34,6 +34,7 @@ def cast_back_e5m6(
     assert x_sf.dtype in (torch.int32, torch.float32)
     assert data.dtype == torch.uint8
     hidden = data.size(1) * 2 // 3
-    assert hidden % 8 == 0
+    # the dequantisation kernel works on 16 values per lane (the cast itself accepts hidden % 8 == 0)
+    assert hidden % 16 == 0, 'cast_back_e5m6 needs hidden % 16 == 0'
     data, x_sf, in_config = get_cast_input_and_config((data, x_sf), tuple(x_block_size))
     return launch_cast_back(data, _lib.FMT_E5M6, x_sf, in_config, num_tokens, hidden, fmt)
