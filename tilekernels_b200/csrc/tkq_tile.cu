@@ -45,6 +45,7 @@ struct TileParams {
     uint32_t flags;
     float clamp_min;
     bool fast_pow2;
+    const int32_t* pos_to_token;  // direct per-channel cast only: output row i reads x row pos_to_token[i] (negative: zeros)
 };
 
 template <int DT>
@@ -346,6 +347,7 @@ __device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
 // the eight warps through shared memory, where thread j < 128 finishes column j, computes its scale once and
 // leaves the inverse for the conversion pass.  Two barriers per tile, nothing staged.
 // ---------------------------------------------------------------------------
+template <bool kGather>
 __global__ void __launch_bounds__(kTileThreads, 4) per_channel_cast_direct_kernel(const TileParams p, const bool wide) {
     __shared__ __align__(16) uint32_t warp_colmax[kTileThreads / 32][kTile / 2];
     __shared__ __align__(16) float col_inv[kTile];
@@ -360,7 +362,13 @@ __global__ void __launch_bounds__(kTileThreads, 4) per_channel_cast_direct_kerne
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int r = r_base + 32 * k;
-            if (col_ok && r < c.valid_rows) PlainSource<TKQ_DT_BF16>::issue(raw[k], xb + ((c.row0 + r) * p.hidden + c.col0 + c16 * 16) * 2, wide);
+            int64_t src_row = c.row0 + r;
+            bool ok = col_ok && r < c.valid_rows;
+            if (kGather && ok) {
+                src_row = p.pos_to_token[c.row0 + r];
+                ok = src_row >= 0;
+            }
+            if (ok) PlainSource<TKQ_DT_BF16>::issue(raw[k], xb + (src_row * p.hidden + c.col0 + c16 * 16) * 2, wide);
             else PlainSource<TKQ_DT_BF16>::zero(raw[k]);
         }
         uint32_t cm[8];
@@ -1164,7 +1172,7 @@ extern "C" int tkq_per_channel_cast(const void* x, int in_dtype, int64_t num_tok
     // bf16: the direct kernel, except for the largest shapes, where the staged light kernel (six blocks per SM)
     // measured a little faster (118 against 121 us on [32768, 7168]; 11.6 against 10.4 us on [7168, 2048])
     if (in_dtype == TKQ_DT_BF16 && (num_tokens / kTile) * p.tiles_k <= int64_t{64} * device_sm_count())
-        return launch_tile_direct(per_channel_cast_direct_kernel, p, 4, "per_channel_cast", s);
+        return launch_tile_direct(per_channel_cast_direct_kernel<false>, p, 4, "per_channel_cast", s);
     return in_dtype == TKQ_DT_BF16
                ? launch_tile_light<TKQ_DT_BF16>(per_channel_cast_light_kernel<TKQ_DT_BF16>, p, "per_channel_cast", s)
                : launch_tile(per_channel_cast_kernel<TKQ_DT_FP32>, p, 4, "per_channel_cast", s);
@@ -1204,9 +1212,25 @@ extern "C" int tkq_per_channel_cast_fused(const void* x, int in_kind, const floa
     const int64_t tiles = ((num_tokens_out + kTile - 1) / kTile) * p.tiles_k;
     if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in_kind == TKQ_DT_BF16) {
+        // bf16 rows, gathered or not: the direct per-channel kernel (packed column maxima), rows through pos_to_token
+        TileParams q{};
+        q.x = x;
+        q.out = p.out;
+        q.sf = sf;
+        q.num_tokens = num_tokens_out;
+        q.hidden = hidden;
+        q.sf_stride = hidden;
+        q.tiles_k = p.tiles_k;
+        q.flags = flags;
+        q.clamp_min = p.clamp_min;
+        q.fast_pow2 = p.fast_pow2;
+        q.pos_to_token = pos_to_token;
+        return pos_to_token != nullptr ? launch_tile_direct(per_channel_cast_direct_kernel<true>, q, 4, "per_channel_cast_fused", s)
+                                       : launch_tile_direct(per_channel_cast_direct_kernel<false>, q, 4, "per_channel_cast_fused", s);
+    }
     const unsigned grid = static_cast<unsigned>(tiles);
-    if (in_kind == TKQ_DT_BF16) per_channel_cast_fused_kernel<TKQ_DT_BF16><<<grid, kTileThreads, 0, s>>>(p);
-    else if (in_kind == TKQ_DT_FP32) per_channel_cast_fused_kernel<TKQ_DT_FP32><<<grid, kTileThreads, 0, s>>>(p);
+    if (in_kind == TKQ_DT_FP32) per_channel_cast_fused_kernel<TKQ_DT_FP32><<<grid, kTileThreads, 0, s>>>(p);
     else per_channel_cast_fused_kernel<kInFp8><<<grid, kTileThreads, 0, s>>>(p);
     return check_launch("per_channel_cast_fused");
 }
