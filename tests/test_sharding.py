@@ -64,3 +64,21 @@ def test_two_ranks_reproduce_the_unsharded_cast(tmp_path, oracle):
     assert parts[0]['start'] == 0 and parts[0]['stop'] == parts[1]['start'] and parts[1]['stop'] == rows
     assert torch.equal(torch.cat([p['out'] for p in parts]), out.view(torch.uint8))
     assert torch.equal(torch.cat([p['sf'] for p in parts]), sf.contiguous())
+
+
+def test_benchmark_shard_parity_check(oracle):
+    """The check the benchmark runs on every rank (first and last 4096-row band of the shard against the CPU checker)
+    accepts the correct outputs and rejects a single wrong code or scale byte in either band."""
+    sys.path.insert(0, ROOT)
+    import bench
+    from tilekernels_b200.testing import make_config_input
+    rows = 8192 + 512
+    x = make_config_input('cfg5', rows)
+    out, sf = oracle.cast(x, 'e4m3', (1, 128), round_sf=True, use_tma_aligned_col_major_sf=True, use_packed_ue8m0=True)
+    assert bench.shard_parity(torch, oracle, x, out, sf, rows)
+    bad = out.clone()
+    bad.view(torch.uint8)[rows - 1, 7] ^= 1
+    assert not bench.shard_parity(torch, oracle, x, bad, sf, rows)
+    bad_sf = sf.clone()
+    bad_sf[0, 0] += 1
+    assert not bench.shard_parity(torch, oracle, x, out, bad_sf, rows)

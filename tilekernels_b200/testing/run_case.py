@@ -3,7 +3,7 @@
 
     python -m tilekernels_b200.testing.run_case --op cfg5 --rows 32768 --launches 3
 
-ops: cfg1 (per-token e4m3, fp32 scales), cfg2_block, cfg2_channel, cfg3 (SwiGLU + cast), cfg4_fp4, cfg4_e5m6,
+ops: cfg1 (per-token e4m3, fp32 scales), cfg2_block, cfg2_channel, cfg3 (SwiGLU + cast; cfg3_ue8m0 with power-of-two scales), cfg4_fp4, cfg4_e5m6,
 cfg5 (per-token e4m3, ue8m0 scales), back_e4m3 / back_e5m6 (dequantisation of cfg4's tensor to bf16), bwd (SwiGLU
 backward + cast on cfg3's tensor quantised with power-of-two scales), expand (row expansion of cfg1's FP8 cast with
 ue8m0 scales to 8 positions per token), requant (per-token e4m3 cast of cfg4's tensor already quantised per 128x128 block
@@ -21,6 +21,8 @@ OPS = {
     'cfg2_block': ('cfg2', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128))),
     'cfg2_channel': ('cfg2', lambda x: quant.per_channel_cast(x, 'e4m3', 128)),
     'cfg3': ('cfg3', lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128)),
+    'cfg3_ue8m0': ('cfg3', lambda x: quant.swiglu_forward_and_per_token_cast(x, 'e4m3', 128, use_tma_aligned_col_major_sf=True, round_sf=True,
+                                                                              use_packed_ue8m0=True)),
     'cfg4_fp4': ('cfg4', lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)),
     'cfg4_e5m6': ('cfg4', lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1])),
     'back_e4m3': ('cfg4', lambda q: (quant.cast_back(q, 'bf16', (1, 128)),)),
