@@ -106,12 +106,6 @@ def test_swiglu_forward_and_per_token_cast(oracle, cuda_device, num_tokens, hidd
             assert torch.equal(counts.cpu(), counts_ref)
 
 
-def test_overall_code_difference_rate():
-    """Over every approximate case above together: far below the 1e-4 the rule allows."""
-    assert _totals['cases'] > 0 and _totals['codes'] > 10 ** 7
-    assert _totals['differing'] <= 1e-5 * _totals['codes'], _totals
-
-
 @pytest.mark.parametrize('hidden', [512, 2048])
 @pytest.mark.parametrize('clamp_min', [1e-2, 1e-20, 1e-35])
 def test_custom_sf_clamp_min(oracle, cuda_device, hidden, clamp_min):
@@ -204,3 +198,26 @@ def test_swiglu_forward_and_per_channel_cast_and_transpose(oracle, cuda_device, 
         out_ref = out_ref.view(torch.uint8).T.contiguous().view(torch.float8_e4m3fn)
     assert_equal(to_host(sf), sf_ref)
     assert_equal(to_host(out), out_ref)
+
+
+@pytest.mark.parametrize('flags', [(False, False, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('hidden', [1024, 1152, 2176, 4096, 7168, 16384])
+def test_row_segments_of_the_staged_kernel(oracle, cuda_device, hidden, flags):
+    """Rows longer and shorter than one 2048-activation segment, with full and partly filled last segments."""
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    gen = torch.Generator().manual_seed(hidden)
+    x_cpu = (torch.randn((37, 2 * hidden), generator=gen) * 2).to(torch.bfloat16)
+    out, sf = quant.swiglu_forward_and_per_token_cast(x_cpu.to(cuda_device), 'e4m3', 128, use_tma_aligned_col_major_sf=col,
+                                                      round_sf=rnd, use_packed_ue8m0=ue)
+    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x_cpu), 'e4m3', (1, 128), use_tma_aligned_col_major_sf=col, round_sf=rnd,
+                                  use_packed_ue8m0=ue)
+    assert_equal(to_host(sf), sf_ref)
+    _check_codes(to_host(out).view(torch.uint8), out_ref.view(torch.uint8), exact=False)
+
+
+def test_zz_overall_code_difference_rate():
+    """Over every approximate case of this file together (it runs last): far below the 1e-4 the rule allows."""
+    if _totals['codes'] < 10 ** 7:
+        pytest.skip('needs the parametrised cases of this file to have run in the same process')
+    assert _totals['differing'] <= 1e-5 * _totals['codes'], _totals
