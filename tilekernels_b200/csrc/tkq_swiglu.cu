@@ -25,26 +25,18 @@ static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t 
     constexpr int kStages = 2;
     const int smem = kStages * kSwStageBytes;
     p.total_items = static_cast<uint32_t>(total);
-    // Resident blocks per SM.  Items are dealt round-robin, so the last round is only as full as total / grid allows,
-    // and on B200 fewer concurrent row streams use the DRAM better while the exact pass wants many warps: with
-    // power-of-two scales (exact pass almost never taken) 8..12 blocks are tried, otherwise 10..12, and the count with
-    // the fullest last round wins (measured on [16384, 2 x 2048]: 29.7 us with 8 blocks against 32.9 us with 12 for
-    // power-of-two scales; 32.3 us with 12 against 34.8 us with 8 for fp32 scales).
+    // Resident blocks per SM, measured on B200 (CUDA-graph replay, rows x [2 x 2048], us for 8 / 10 / 12 blocks):
+    //   power-of-two scales (exact pass almost never taken)   8192 rows 16.5 / 15.8 / 16.6;  16384 rows 29.5 / 29.9 / 32.6;
+    //                                                          32768 rows 55.8 / 56.8 / 60.9   (odd counts are worse: 7: 32.4, 9: 31.2)
+    //   fp32 scales (exact pass on every group wants warps)    8192 rows 18.7 / 17.8 / 17.5;  16384 rows 34.3 / 33.0 / 32.3;
+    //                                                          32768 rows 64.2 / 61.9 / 60.1
+    // so: fp32 scales take all 12; power-of-two scales take 8 when every block then still gets 10 or more items, else 10.
     const int occ = cached_occupancy(reinterpret_cast<const void*>(kernel), kSwThreads, smem);
     int sms = device_sm_count();
     if (sm_limit > 0) sms = std::min(sms, sm_limit);
-    const int k_max = std::max(1, std::min(occ, 12)), k_min = std::min(k_max, p.fast_pow2 ? 8 : 10);
-    int best_k = k_max;
-    double best_fill = 0.0;
-    for (int k = k_min; k <= k_max; ++k) {
-        const int64_t blocks = static_cast<int64_t>(sms) * k;
-        const int64_t rounds = (total + blocks - 1) / blocks;
-        const double fill = static_cast<double>(total) / static_cast<double>(rounds * blocks);
-        if (fill > best_fill + 0.01 || (!p.fast_pow2 && fill > best_fill - 0.01)) {  // ties: fewer blocks / more blocks
-            best_fill = std::max(fill, best_fill);
-            best_k = k;
-        }
-    }
+    int best_k = 12;
+    if (p.fast_pow2) best_k = total >= int64_t{10} * 8 * sms ? 8 : 10;
+    best_k = std::max(1, std::min(best_k, occ));
     const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(total, static_cast<int64_t>(sms) * best_k)));
     kernel<<<grid, kSwThreads, smem, stream>>>(p, static_cast<uint32_t>(nseg), kStages);
     return check_launch("swiglu_forward_and_per_token_cast (staged kernel)");
