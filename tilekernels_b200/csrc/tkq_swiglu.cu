@@ -14,9 +14,9 @@ static bool pipeline_applies(const TokenCastParams& p, int in_dtype, bool per_ro
     return in_dtype == TKQ_DT_BF16 && !per_row_scale && p.hidden >= 1024 && p.clamp_min >= 1e-30f && !(flags & TKQ_EXACT_CODES);
 }
 
-template <int kClampMode>
+template <int kClampMode, bool kRouted, bool kFull>
 static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t stream) {
-    auto kernel = swiglu_group_pipeline_kernel<kClampMode>;
+    auto kernel = swiglu_group_pipeline_kernel<kClampMode, kRouted, kFull>;
     const int64_t nseg = (p.hidden + kSwSegment - 1) / kSwSegment;
     const int64_t total = p.num_tokens * nseg;
     if (total >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "more than 2^31 work items; split the token dimension");
@@ -42,10 +42,18 @@ static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t 
     return check_launch("swiglu_forward_and_per_token_cast (staged kernel)");
 }
 
+template <bool kRouted, bool kFull>
+static int dispatch_swiglu_pipeline_clamp(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
+    if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0, kRouted, kFull>(p, sm_limit, stream);
+    if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1, kRouted, kFull>(p, sm_limit, stream);
+    return launch_swiglu_pipeline<2, kRouted, kFull>(p, sm_limit, stream);
+}
+
 static int dispatch_swiglu_pipeline(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
-    if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0>(p, sm_limit, stream);
-    if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1>(p, sm_limit, stream);
-    return launch_swiglu_pipeline<2>(p, sm_limit, stream);
+    const bool routed = p.pos_to_expert != nullptr || p.pos_to_token_topk != nullptr;
+    const bool full = p.hidden % kSwSegment == 0;
+    if (routed) return full ? dispatch_swiglu_pipeline_clamp<true, true>(p, sm_limit, stream) : dispatch_swiglu_pipeline_clamp<true, false>(p, sm_limit, stream);
+    return full ? dispatch_swiglu_pipeline_clamp<false, true>(p, sm_limit, stream) : dispatch_swiglu_pipeline_clamp<false, false>(p, sm_limit, stream);
 }
 
 int swiglu_wait_flag() {

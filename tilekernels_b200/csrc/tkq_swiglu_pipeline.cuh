@@ -190,7 +190,9 @@ __device__ __forceinline__ void quantize_e4m3x8(const float* v, float inv, uint3
 // order, and one load instruction of the warp touches every shared-memory bank exactly once.  32 activations per
 // lane and item share ONE group reduction, ONE exact evaluation (the flagged piece: 8 pairs = 4 lanes x 2), one
 // scale.
-template <int kClampMode>
+// kRouted: the call passes an expert mask and / or row weights (the plain form compiles without their checks)
+// kFull:   hidden is a multiple of 2048, so every item is a full segment and every lane always has data
+template <int kClampMode, bool kRouted, bool kFull>
 __global__ void __launch_bounds__(kSwThreads, 12)
 swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const uint32_t stages) {
     extern __shared__ __align__(128) uint8_t ring[];
@@ -227,7 +229,7 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
     auto produce = [&](uint32_t limit) {
         while (p_loads < limit && p_item < total) {
             const uint32_t row = nseg == 1 ? p_item : p_item / nseg, seg = p_item - row * nseg;
-            if (p.pos_to_expert == nullptr || p.pos_to_expert[row] >= 0) {
+            if (!kRouted || p.pos_to_expert == nullptr || p.pos_to_expert[row] >= 0) {
                 const uint32_t col0 = seg * kSwSegment;
                 const uint32_t bytes = min(static_cast<uint32_t>(kSwSegment), hidden - col0) * 2u;
                 uint8_t* dst = ring + static_cast<size_t>(p_stage) * kSwStageBytes;
@@ -246,7 +248,7 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
     uint32_t loads = 0, stage = 0, phase = 0;
     for (uint32_t item = blockIdx.x; item < total; item += gridDim.x) {
         const uint32_t row = nseg == 1 ? item : item / nseg, seg = item - row * nseg;
-        if (p.pos_to_expert != nullptr && p.pos_to_expert[row] < 0) continue;  // block-uniform
+        if (kRouted && p.pos_to_expert != nullptr && p.pos_to_expert[row] < 0) continue;  // block-uniform
         // every thread is done with the stage of the previous load (its reads ordered before the refill)
         fence_proxy_async_smem();
         __syncthreads();
@@ -269,11 +271,11 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
         phase ^= stage == 0 ? 1u : 0u;
 
         const uint32_t seg_col = seg * kSwSegment;
-        const uint32_t width = min(static_cast<uint32_t>(kSwSegment), hidden - seg_col);  // a multiple of 128
-        if (warp * 1024 >= width) continue;     // warp-uniform: this warp's columns lie beyond the row
-        const bool active = group_col < width;  // whole groups (4 lanes) are active or not
+        const uint32_t width = kFull ? kSwSegment : min(static_cast<uint32_t>(kSwSegment), hidden - seg_col);  // a multiple of 128
+        if (!kFull && warp * 1024 >= width) continue;     // warp-uniform: this warp's columns lie beyond the row
+        const bool active = kFull || group_col < width;  // whole groups (4 lanes) are active or not
         float w = 1.0f;
-        if (p.pos_to_token_topk != nullptr) {
+        if (kRouted && p.pos_to_token_topk != nullptr) {
             const int32_t pos = p.pos_to_token_topk[row];
             w = pos >= 0 ? p.topk_weights[pos] : 0.0f;
         }
@@ -290,6 +292,10 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
                 uw = *reinterpret_cast<const uint4*>(st + kSwHalfBytes + off);
             }
             piece_max[k] = swiglu_approx_octet<kClampMode>(gw, uw, clamp, w, cnt, y[k], g_min);
+            // keep the four pieces apart in the instruction schedule: left alone, the compiler interleaves all of them,
+            // runs out of registers and spills (49 us instead of 32 us on [16384, 2 x 2048]; with 96 registers for ten
+            // resident blocks it still spilled and took 34.6 us)
+            if (kFull) asm volatile("" ::: "memory");
         }
 
         float amax;
