@@ -216,6 +216,47 @@ def test_row_segments_of_the_staged_kernel(oracle, cuda_device, hidden, flags):
     _check_codes(to_host(out).view(torch.uint8), out_ref.view(torch.uint8), exact=False)
 
 
+@pytest.mark.parametrize('seed', range(24))
+def test_random_shapes_and_options_of_the_staged_kernel(oracle, cuda_device, seed):
+    """Seeded random draws of everything the staged kernel depends on: tokens, hidden (any multiple of 128 from 1024),
+    scale layout, clamp, counters, row weights, expert mask, input scale."""
+    from tilekernels_b200 import quant
+    gen = torch.Generator().manual_seed(1000 + seed)
+    draw = lambda n: int(torch.randint(0, n, (1,), generator=gen))
+    num_tokens = (1, 2, 7, 64, 129, 777, 1500)[draw(7)]
+    hidden = 128 * (8 + draw(57))
+    col, rnd, ue = ((False, False, False), (False, True, False), (True, True, False), (True, True, True))[draw(4)]
+    clamp = (None, None, 10.0, 1.0, 0.25)[draw(5)]
+    weighted, masked, count = draw(2) == 1 and not ue, draw(2) == 1, clamp is not None and draw(2) == 1
+    x_cpu = (torch.randn((num_tokens, 2 * hidden), generator=gen) * (0.05, 1.0, 3.0, 20.0)[draw(4)]).to(torch.bfloat16)
+    pos_to_expert, pos_to_token_topk, weights = _routing(num_tokens, gen)
+    if masked:
+        x_cpu[pos_to_expert < 0] = 0
+    counts_ref = torch.zeros(3, dtype=torch.int64)
+    y = oracle.swiglu_forward(x_cpu, pos_to_token_topk if weighted else None, weights if weighted else None, clamp,
+                              counts_ref if count else None)
+    mask = (pos_to_expert < 0).unsqueeze(-1) if masked else torch.zeros((num_tokens, 1), dtype=torch.bool)
+    out_ref, sf_ref = oracle.cast(y.masked_fill(mask, 0), 'e4m3', (1, 128), use_tma_aligned_col_major_sf=col, round_sf=rnd,
+                                  use_packed_ue8m0=ue)
+    counts = torch.zeros(3, dtype=torch.int64, device=cuda_device) if count else None
+    out, sf = quant.swiglu_forward_and_per_token_cast(
+        x_cpu.to(cuda_device), 'e4m3', 128,
+        pos_to_token_topk=pos_to_token_topk.to(cuda_device) if weighted else None,
+        topk_weights=weights.to(cuda_device) if weighted else None,
+        pos_to_expert=pos_to_expert.to(cuda_device) if masked else None,
+        use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue, swiglu_clamp_value=clamp, clamped_count=counts)
+    sf_h, sf_r = to_host(sf).clone(), sf_ref.clone()
+    sf_h[mask.expand_as(sf_h)] = 0
+    sf_r[mask.expand_as(sf_r)] = 0
+    assert_equal(sf_h, sf_r)
+    if count:
+        # rows the mask skips are not counted by the kernel; the oracle saw them as zeros, which no clamp touches
+        assert torch.equal(counts.cpu(), counts_ref)
+    diff = (to_host(out).view(torch.uint8).masked_fill(mask, 0).to(torch.int32) -
+            out_ref.view(torch.uint8).masked_fill(mask, 0).to(torch.int32)).abs()
+    assert int(diff.max()) <= 1 and int((diff > 0).sum()) <= max(2, int(1e-4 * diff.numel()))
+
+
 def test_zz_overall_code_difference_rate():
     """Over every approximate case of this file together (it runs last): far below the 1e-4 the rule allows."""
     if _totals['codes'] < 10 ** 7:
