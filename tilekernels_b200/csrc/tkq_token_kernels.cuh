@@ -527,14 +527,17 @@ __global__ void __launch_bounds__(kRowMaxThreads) e5m6_row_pipeline_kernel(const
 // ---------------------------------------------------------------------------
 // Host side: geometry of a group_cast_kernel launch.
 // ---------------------------------------------------------------------------
+// max_blocks_per_sm > 0 caps the resident blocks per SM below what the occupancy allows.
 template <class Kernel>
-int launch_group_kernel(Kernel kernel, TokenCastParams p, int unroll, int sm_limit, cudaStream_t stream, const char* what) {
+int launch_group_kernel(Kernel kernel, TokenCastParams p, int unroll, int sm_limit, cudaStream_t stream, const char* what,
+                        int max_blocks_per_sm = 0) {
     const int64_t steps = (p.hidden + 511) / 512;
     const int64_t items_per_row = (steps + unroll - 1) / unroll;
     const int64_t total = p.num_tokens * items_per_row;
     if (total >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "more than 2^31 work items; split the token dimension");
     constexpr int kWarpsPerBlock = kGroupThreads / 32;
-    const int grid = grid_size(kernel, kGroupThreads, (total + kWarpsPerBlock - 1) / kWarpsPerBlock, 0, sm_limit);
+    int grid = grid_size(kernel, kGroupThreads, (total + kWarpsPerBlock - 1) / kWarpsPerBlock, 0, sm_limit);
+    if (max_blocks_per_sm > 0) grid = static_cast<int>(std::min<int64_t>(grid, static_cast<int64_t>(device_sm_count()) * max_blocks_per_sm));
     const uint32_t nwarps = static_cast<uint32_t>(grid) * kWarpsPerBlock;
     p.items_per_row = static_cast<uint32_t>(items_per_row);
     p.total_items = static_cast<uint32_t>(total);
