@@ -122,3 +122,31 @@ def test_per_block_cast_lossless_reports_range_violation(cuda_device):
     quant.per_block_cast_lossless((q, qsf), 'e4m3', (1, 32), (128, 128), False, True, False)
     assert lib.tkq_device_error() == 2
     assert lib.tkq_device_error() == 0
+
+
+@pytest.mark.parametrize('op', ['per_block', 'per_channel', 'per_channel_gather'])
+def test_direct_tile_kernels_with_16_byte_aligned_input(oracle, cuda_device, op):
+    """The direct kernels read 32 bytes per lane with one 256-bit load when the tensor starts on a 32-byte boundary
+    and with two 128-bit loads otherwise: a contiguous tensor that starts 16 bytes into an allocation takes the second
+    form and must give the same bytes."""
+    from tilekernels_b200 import quant
+    g = torch.Generator().manual_seed(77)
+    x_cpu = torch.randn((384, 576), generator=g).to(torch.bfloat16)
+    buf = torch.empty(x_cpu.numel() + 8, dtype=torch.bfloat16, device=cuda_device)
+    x = buf[8:].view(384, 576)
+    x.copy_(x_cpu)
+    assert x.data_ptr() % 32 == 16 and x.is_contiguous()
+    if op == 'per_block':
+        out, sf = quant.per_block_cast(x, 'e4m3', (128, 128))
+        out_ref, sf_ref = oracle.cast(x_cpu, 'e4m3', (128, 128))
+    elif op == 'per_channel':
+        out, sf = quant.per_channel_cast(x, 'e4m3', 128)
+        out_ref, sf_ref = oracle.cast(x_cpu, 'e4m3', (128, 1))
+    else:
+        pos = torch.randint(0, 384, (256,), generator=g, dtype=torch.int32)
+        pos[::5] = -1
+        out, sf = quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, pos.to(cuda_device))
+        gathered = torch.where((pos >= 0).unsqueeze(-1), x_cpu[pos.clamp_min(0).long()], torch.zeros((), dtype=torch.bfloat16))
+        out_ref, sf_ref = oracle.cast(gathered, 'e4m3', (128, 1))
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)
