@@ -14,9 +14,9 @@ static bool pipeline_applies(const TokenCastParams& p, int in_dtype, bool per_ro
     return in_dtype == TKQ_DT_BF16 && !per_row_scale && p.hidden >= 1024 && p.clamp_min >= 1e-30f && !(flags & TKQ_EXACT_CODES);
 }
 
-template <int kClampMode, bool kRouted, bool kFull>
+template <int kClampMode, bool kRouted, bool kFull, bool kPairs>
 static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t stream) {
-    auto kernel = swiglu_group_pipeline_kernel<kClampMode, kRouted, kFull>;
+    auto kernel = swiglu_group_pipeline_kernel<kClampMode, kRouted, kFull, kPairs>;
     const int64_t nseg = (p.hidden + kSwSegment - 1) / kSwSegment;
     const int64_t total = p.num_tokens * nseg;
     if (total >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "more than 2^31 work items; split the token dimension");
@@ -25,17 +25,20 @@ static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t 
     constexpr int kStages = 2;
     const int smem = kStages * kSwStageBytes;
     p.total_items = static_cast<uint32_t>(total);
-    // Resident blocks per SM, measured on B200 (CUDA-graph replay, rows x [2 x 2048], us for 8 / 10 / 12 blocks):
-    //   power-of-two scales (exact pass almost never taken)   8192 rows 16.5 / 15.8 / 16.6;  16384 rows 29.5 / 29.9 / 32.6;
+    // Resident blocks per SM, measured on B200 (CUDA-graph replay, rows x [2 x 2048], us for 8 / 10 / 12 blocks of the
+    // 79-register instantiation):
+    //   power-of-two scales (exact pass almost never taken)   8192 rows 16.5 / 15.8 / 16.6;  16384 rows 28.5 / 29.9 / 32.6;
     //                                                          32768 rows 55.8 / 56.8 / 60.9   (odd counts are worse: 7: 32.4, 9: 31.2)
-    //   fp32 scales (exact pass on every group wants warps)    8192 rows 18.7 / 17.8 / 17.5;  16384 rows 34.3 / 33.0 / 32.3;
+    //   fp32 scales (exact pass on every group wants warps)    8192 rows 18.7 / 17.8 / 17.5;  16384 rows 34.3 / 33.0 / 32.0;
     //                                                          32768 rows 64.2 / 61.9 / 60.1
-    // so: fp32 scales take all 12; power-of-two scales take 8 when every block then still gets 10 or more items, else 10.
+    // and 30.5 us (16384 rows) for fp32 scales with 10 blocks of the instantiation that interleaves pieces in pairs.
+    // So: fp32 scales take that instantiation with 10 blocks; power-of-two scales the other one with 8 blocks when every
+    // block then still gets 10 or more items, else 10.
     const int occ = cached_occupancy(reinterpret_cast<const void*>(kernel), kSwThreads, smem);
     int sms = device_sm_count();
     if (sm_limit > 0) sms = std::min(sms, sm_limit);
-    int best_k = 12;
-    if (p.fast_pow2) best_k = total >= int64_t{10} * 8 * sms ? 8 : 10;
+    int best_k = 10;
+    if (!kPairs) best_k = total >= int64_t{10} * 8 * sms ? 8 : 10;
     best_k = std::max(1, std::min(best_k, occ));
     const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(total, static_cast<int64_t>(sms) * best_k)));
     kernel<<<grid, kSwThreads, smem, stream>>>(p, static_cast<uint32_t>(nseg), kStages);
@@ -44,9 +47,14 @@ static int launch_swiglu_pipeline(TokenCastParams p, int sm_limit, cudaStream_t 
 
 template <bool kRouted, bool kFull>
 static int dispatch_swiglu_pipeline_clamp(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {
-    if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0, kRouted, kFull>(p, sm_limit, stream);
-    if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1, kRouted, kFull>(p, sm_limit, stream);
-    return launch_swiglu_pipeline<2, kRouted, kFull>(p, sm_limit, stream);
+    if (p.fast_pow2) {
+        if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0, kRouted, kFull, false>(p, sm_limit, stream);
+        if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1, kRouted, kFull, false>(p, sm_limit, stream);
+        return launch_swiglu_pipeline<2, kRouted, kFull, false>(p, sm_limit, stream);
+    }
+    if (p.swiglu_clamp < 0.0f) return launch_swiglu_pipeline<0, kRouted, kFull, true>(p, sm_limit, stream);
+    if (p.clamped_count == nullptr) return launch_swiglu_pipeline<1, kRouted, kFull, true>(p, sm_limit, stream);
+    return launch_swiglu_pipeline<2, kRouted, kFull, true>(p, sm_limit, stream);
 }
 
 static int dispatch_swiglu_pipeline(const TokenCastParams& p, int sm_limit, cudaStream_t stream) {

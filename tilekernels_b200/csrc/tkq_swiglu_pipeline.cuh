@@ -192,8 +192,12 @@ __device__ __forceinline__ void quantize_e4m3x8(const float* v, float inv, uint3
 // scale.
 // kRouted: the call passes an expert mask and / or row weights (the plain form compiles without their checks)
 // kFull:   hidden is a multiple of 2048, so every item is a full segment and every lane always has data
-template <int kClampMode, bool kRouted, bool kFull>
-__global__ void __launch_bounds__(kSwThreads, 12)
+// kPairs:  the instruction schedule may interleave the lane's four pieces two at a time (about 95 registers, ten resident
+//          blocks per SM) instead of one at a time (79 registers, twelve blocks).  Measured on [16384, 2 x 2048]: fp32
+//          scales, whose exact pass needs the slack, 30.5 us in pairs with 10 blocks against 32.0 us singly with 12;
+//          power-of-two scales 28.5 us singly with 8 blocks against 30.6 us in pairs with 10
+template <int kClampMode, bool kRouted, bool kFull, bool kPairs>
+__global__ void __launch_bounds__(kSwThreads, kPairs ? 10 : 12)
 swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const uint32_t stages) {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full_bar[kSwMaxStages];
@@ -292,10 +296,10 @@ swiglu_group_pipeline_kernel(const TokenCastParams p, const uint32_t nseg, const
                 uw = *reinterpret_cast<const uint4*>(st + kSwHalfBytes + off);
             }
             piece_max[k] = swiglu_approx_octet<kClampMode>(gw, uw, clamp, w, cnt, y[k], g_min);
-            // keep the four pieces apart in the instruction schedule: left alone, the compiler interleaves all of them,
-            // runs out of registers and spills (49 us instead of 32 us on [16384, 2 x 2048]; with 96 registers for ten
-            // resident blocks it still spilled and took 34.6 us)
-            if (kFull) asm volatile("" ::: "memory");
+            // keep the pieces apart in the instruction schedule (one by one, or two by two with kPairs): left alone, the
+            // compiler interleaves all four, runs out of registers and spills (49 us instead of 32 us on
+            // [16384, 2 x 2048]; with 96 registers for ten resident blocks it still spilled and took 34.6 us)
+            if (kFull && (!kPairs || (k & 1))) asm volatile("" ::: "memory");
         }
 
         float amax;
