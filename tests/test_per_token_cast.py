@@ -119,7 +119,7 @@ def test_misaligned_view_uses_narrow_loads(oracle, cuda_device):
 
 
 def _requant_params():
-    for num_tokens, hidden in ((4001, 576), (4001, 7168), (129, 2048), (33, 4096)):
+    for num_tokens, hidden in ((4001, 576), (4001, 7168), (129, 2048), (33, 4096), (65, 1536)):
         for in_fmt in ('e4m3', 'e2m1'):
             for xb in ((128, 128), (32, 32)):
                 for g in (32, 128):

@@ -96,20 +96,24 @@ __device__ __forceinline__ void flush_clamp_counters(const ClampCounters& cnt, u
 }
 
 // kClampMode: 0 = no clamp, 1 = clamp, 2 = clamp and count (SwiGLU sources only)
-template <class Src, int kKind, int FMT, int LPG, int U, int kClampMode>
+// kLean: the flags are known at compile time to be the common production set -- power-of-two scales by the
+//        division-free path, packed ue8m0 in the column-major layout, data and scales both written -- so that their
+//        tests leave the loop.  Only the re-quantising cast is instantiated so (101 -> 93 us on [32768, 7168]); the
+//        plain bf16 casts run slower in this form (cfg5 0.954 ms against 0.894 ms, FP4 97 us against 95 us)
+template <class Src, int kKind, int FMT, int LPG, int U, int kClampMode, bool kLean = false>
 __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCastParams p) {
     constexpr bool kSwiglu = kKind == kSourceSwiglu;
     constexpr bool kQuant = kKind == kSourceQuant;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
-    const bool round_sf = p.flags & TKQ_ROUND_SF;
-    const bool col_major = p.flags & TKQ_SF_COL_MAJOR;
-    const bool ue8m0 = p.flags & TKQ_SF_UE8M0;
-    const bool sf_only = p.flags & TKQ_SF_ONLY;
-    const bool cast_only = p.flags & TKQ_CAST_ONLY;
+    const bool round_sf = kLean || (p.flags & TKQ_ROUND_SF);
+    const bool col_major = kLean || (p.flags & TKQ_SF_COL_MAJOR);
+    const bool ue8m0 = kLean || (p.flags & TKQ_SF_UE8M0);
+    const bool sf_only = !kLean && (p.flags & TKQ_SF_ONLY);
+    const bool cast_only = !kLean && (p.flags & TKQ_CAST_ONLY);
     const bool wide = p.wide_loads;
-    const bool fast_pow2 = p.fast_pow2;
+    const bool fast_pow2 = kLean || p.fast_pow2;
     const uint32_t hidden = static_cast<uint32_t>(p.hidden);
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
     ClampCounters cnt;
@@ -550,6 +554,11 @@ int launch_group_kernel(Kernel kernel, TokenCastParams p, int unroll, int sm_lim
 // round_sf with a clamp that keeps clamp / MAX a normal number: the division-free scale path applies.
 inline bool can_use_fast_pow2(unsigned flags, float clamp_min, float max_q) {
     return (flags & TKQ_ROUND_SF) && clamp_min >= max_q * 1.1754943508222875e-38f;
+}
+
+// The flag set the kLean instantiations of group_cast_kernel are compiled for.
+inline bool lean_flags(const TokenCastParams& p) {
+    return p.flags == (TKQ_ROUND_SF | TKQ_SF_COL_MAJOR | TKQ_SF_UE8M0) && p.fast_pow2;
 }
 
 }  // namespace tkq
