@@ -283,6 +283,10 @@ def op_specs(torch, quant, moe, device) -> list:
         spec('per_channel_cast_fused', 'cfg2 gather', 'cfg2', lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gathers[x.shape[0]]),
              fmt='e4m3', rows_out=8192),
         spec('per_channel_cast_and_transpose', 'cfg2', 'cfg2', lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
+        spec('swiglu_forward_and_per_channel_cast_and_transpose', 'cfg3', 'cfg3',
+             lambda x: quant.swiglu_forward_and_per_channel_cast_and_transpose(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
+        spec('per_block_cast_lossless', 'cfg4', 'cfg4', lambda q: quant.per_block_cast_lossless(q, 'e4m3', (1, 32), (128, 128), True, True, True),
+             lambda x: quant.per_token_cast(x, 'e2m1', 32, None, True, True, True), x='e2m1 1x32 ue8m0', fmt='e4m3', block='128x128', sf='ue8m0'),
         spec('swiglu_backward_and_per_token_cast', 'cfg3', 'cfg3', lambda a: quant.swiglu_backward_and_per_token_cast(*a, 128, True),
              backward_inputs, group=128, sf='fp32 pow2', x_sf='pow2'),
         spec('expand_to_fused_with_sf', 'cfg1', 'cfg1', lambda a: moe.expand_to_fused_with_sf(a[0], 128, a[1], a[2], True), expand_inputs,

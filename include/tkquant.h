@@ -202,7 +202,8 @@ int tkq_swiglu_forward_and_per_channel_cast(const void* x, int64_t num_tokens, i
  * reference asserts e_in + 5 >= e_out on the device (exact representability); this library rounds to nearest
  * where that does not hold and raises TKQ_DEVICE_LOSSLESS_RANGE (see tkq_device_error).
  *
- *   x          [num_tokens, hidden / 2] bytes, x_row_stride in VALUES; x_sf as in tkq_per_token_cast_quantized
+ *   x          [num_tokens, hidden / 2] bytes, x_row_stride in VALUES; x_sf as in tkq_per_token_cast_quantized.
+ *              x and every row of it 16-byte aligned (x_row_stride % 32 == 0); fewer than 2^24 values per row
  *   out blocks (1 | 32 | 128) x (32 | 128), multiples of the input block; hidden % 32 == 0
  *   flags      TKQ_SF_COL_MAJOR, TKQ_SF_UE8M0 for the output scales (always powers of two)
  */

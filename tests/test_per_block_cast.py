@@ -105,6 +105,45 @@ def test_per_block_cast_lossless(oracle, cuda_device, num_tokens, hidden, out_bl
     assert_equal(back_out, back_in)
 
 
+def _lossless_block_pairs():
+    yield (1, 16), (1, 32)
+    yield (1, 16), (32, 32)
+    yield (1, 16), (128, 128)
+    yield (1, 32), (32, 128)
+    yield (1, 32), (128, 32)
+    yield (32, 32), (32, 32)
+    yield (32, 32), (128, 128)
+    yield (128, 128), (128, 128)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('flags', [(False, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('in_block,out_block', list(_lossless_block_pairs()), ids=lambda b: f'{b[0]}x{b[1]}')
+@pytest.mark.parametrize('num_tokens,hidden', [(4001, 576), (129, 2048), (300, 7168)])
+def test_per_block_cast_lossless_block_shapes(oracle, cuda_device, num_tokens, hidden, in_block, out_block, flags):
+    """Input blocks other than (1, 32) -- 16 wide (two input scales inside a 32-value piece), 32 x 32, 128 x 128 -- and the
+    mixed output blocks, in both scale layouts; bit-exact against the oracle and lossless."""
+    from tilekernels_b200 import quant
+    g = torch.Generator().manual_seed(num_tokens * 7 + hidden + in_block[1])
+    x = _clamp_abs_ratio(torch.randn((num_tokens, hidden), generator=g) * 2.0 ** torch.randint(-20, 20, (1,), generator=g).item())
+    col, rnd, ue = flags
+    q_ref, qsf_ref = oracle.cast(x, 'e2m1', in_block, round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+    if in_block[0] == 1:
+        q, qsf = quant.per_token_cast(x.to(cuda_device), 'e2m1', in_block[1], None, col, rnd, ue)
+    else:
+        q, qsf = quant.per_block_cast(x.to(cuda_device), 'e2m1', in_block, col, rnd, ue)
+    assert_equal(to_host(q), q_ref)
+    assert_equal(to_host(qsf), qsf_ref)
+    out, sf = quant.per_block_cast_lossless((q, qsf), 'e4m3', in_block, out_block, col, rnd, ue)
+    out_ref, sf_ref = oracle.per_block_cast_lossless((q_ref, qsf_ref), in_block, out_block, col, ue)
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)
+    back_in = oracle.cast_back((q_ref, qsf_ref), 'fp32', in_block)
+    back_out = oracle.cast_back((to_host(out), to_host(sf)), 'fp32', out_block)
+    assert_equal(back_out, back_in)
+
+
+
 def test_per_block_cast_lossless_reports_range_violation(cuda_device):
     """Where the reference's kernel asserts on the device (an input scale more than 2^5 below its output block's
     scale, tile_kernels/quant/per_block_cast_lossless_kernel.py:128), this library finishes the cast and raises

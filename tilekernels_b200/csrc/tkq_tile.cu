@@ -761,73 +761,272 @@ __global__ void __launch_bounds__(kTileThreads) swiglu_per_channel_cast_kernel(c
 // the output is e4m3 with power-of-two scales per (out_bm x out_bk) block.  The output exponent of a block is the
 // largest input exponent inside it minus 6 (not below 0); every value becomes fp4 * 2^(e_in - e_out), which e4m3
 // represents exactly as long as e_in + 5 >= e_out (reference: tile_kernels/quant/per_block_cast_lossless_kernel.py:
-// 96-131; where the reference asserts that condition on the device, this kernel rounds to nearest instead).
-// One block per 128 x 128 tile, plain vector loads, exponent maxima through shared-memory atomics.
+// 96-131; where the reference asserts that condition on the device, this kernel rounds to nearest and counts).
+// Tiles of 128 rows x 256 columns (a row of a tile is 128 bytes of input and 256 bytes of output); a thread owns four
+// 32-value pieces (rows t / 8 + 32 k, columns 32 (t % 8) ..): 16 bytes in, one 32-byte sector out.
 // ---------------------------------------------------------------------------
 struct LosslessParams {
-    TokenCastParams in;  // x, in_sf*, in_block_*, num_tokens, hidden (load_input_scale reads these)
+    TokenCastParams in;  // x, in_sf*, in_block_*, num_tokens, hidden
     void* sf;
     int64_t sf_stride;
-    uint32_t out_bm, out_bk;
-    uint32_t tiles_k;
+    uint32_t tiles_k;    // ceil(hidden / 256)
     uint32_t flags;
+    bool wide_stores;    // out is 32-byte aligned
 };
 
-__global__ void __launch_bounds__(kTileThreads) per_block_cast_lossless_kernel(const LosslessParams p) {
-    __shared__ int exp_max[kTile * 4];  // up to 128 x 4 output blocks per tile (out block 1 x 32)
-    const int t = threadIdx.x;
-    const int c16 = t & 7, r_base = t >> 3;
-    const int64_t hidden = p.in.hidden;
-    const int64_t tile_m = blockIdx.x / p.tiles_k, tile_k = blockIdx.x % p.tiles_k;
-    const int64_t row0 = tile_m * kTile, col0 = tile_k * kTile;
-    const int valid_rows = static_cast<int>(p.in.num_tokens - row0 < kTile ? p.in.num_tokens - row0 : kTile);
-    const int valid_cols = static_cast<int>(hidden - col0 < kTile ? hidden - col0 : kTile);
-    const int nrb = kTile / p.out_bm, ncb = kTile / p.out_bk;
-    for (int i = t; i < nrb * ncb; i += kTileThreads) exp_max[i] = 0;
-    __syncthreads();
+// Resident blocks per SM and tiles copied ahead, measured on B200 for [32768, 7168] with 128 x 128 output blocks (352 MB
+// moved; a device copy of as many bytes takes 54.9 us): 2 blocks / 1 tile ahead 61.6 us, 2 / 2 65.3, 2 / 3 64.8-67.4,
+// 3 / 1 71.3, 3 / 2 71.6, 4 / 1 71.6, 1 / 2 72.3, 1 / 4 73.3, 1 / 8 91.0.  Two thirds of the traffic are writes: more
+// blocks or deeper copies only add streams for the DRAM to interleave.
+constexpr int kLosslessBlocksPerSm = 2;
+constexpr int kLosslessDepth = 1;
+constexpr int kLosslessCols = 256;
 
-    const bool col_ok = c16 * 16 < valid_cols;
-    const int cb = c16 * 16 / p.out_bk;
-    uint32_t e_in[4];
-    QuantSource<TKQ_FMT_E2M1>::Raw raw[4];
+// A thread's part of one tile: the codes of its four pieces and, per piece, the input exponents of its two 16-value halves
+// (equal unless the input blocks are 16 wide).
+struct LosslessPieces {
+    uint4 codes[4];
+    uint32_t e_in[4][2];
+};
+
+// Tiles on their way to a block: every thread copies its own pieces (16 bytes of codes and the aligned words that hold
+// the piece's input scales) to shared memory with asynchronous copies, kLosslessDepth tiles ahead, and reads back only
+// what it copied itself, so that the copies need no barrier, only the thread's own wait_group.  Registers cannot
+// hold that much: with the next tile in registers a thread had 32 bytes in flight and the kernel ran at 0.61 of the
+// copy bandwidth.
+struct LosslessStage {
+    uint4 codes[4][kTileThreads];
+    uint32_t scale_word[2][4][kTileThreads];
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// The aligned 32-bit word that holds the input scale of (row, col): the fp32 scale itself, or four packed ue8m0 bytes.
+__device__ __forceinline__ const uint32_t* input_scale_word(const TokenCastParams& p, uint32_t row, uint32_t col) {
+    const int64_t m = p.in_shift_m1 ? row >> (p.in_shift_m1 - 1) : row / p.in_block_m;
+    const int64_t k = p.in_shift_k1 ? col >> (p.in_shift_k1 - 1) : col / p.in_block_k;
+    if (p.in_sf_flags & TKQ_SF_UE8M0) return reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p.in_sf) + (k >> 2) * p.in_sf_stride + 4 * m);
+    const uint32_t* f = static_cast<const uint32_t*>(p.in_sf);
+    return (p.in_sf_flags & TKQ_SF_COL_MAJOR) ? f + k * p.in_sf_stride + m : f + m * p.in_sf_stride + k;
+}
+
+// kFull: every row and column of the tile exists.  hidden is a multiple of 32, so a piece exists whole or not at all.
+template <bool kFull>
+__device__ __forceinline__ void lossless_issue(const LosslessParams& p, uint32_t tile_m, uint32_t tile_k, int t, int c32, int r_base, LosslessStage& st) {
+    const uint32_t row0 = tile_m * kTile + r_base, col = tile_k * kLosslessCols + c32 * 32;
+    const bool col_ok = kFull || col < static_cast<uint32_t>(p.in.hidden);
+    const bool two_scales = p.in.in_block_k == 16;
+    const uint8_t* src = static_cast<const uint8_t*>(p.in.x) + (static_cast<int64_t>(row0) * p.in.x_stride + col) / 2;
+    const uint32_t pitch = static_cast<uint32_t>(p.in.x_stride) * 16u;  // bytes between a thread's pieces: 32 rows of packed FP4
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const int r = r_base + 32 * k;
-        e_in[k] = 0;
-        QuantSource<TKQ_FMT_E2M1>::zero(raw[k]);
-        if (col_ok && r < valid_rows) {
-            const int64_t elem = (row0 + r) * p.in.x_stride + col0 + c16 * 16;
-            QuantSource<TKQ_FMT_E2M1>::issue(raw[k], static_cast<const uint8_t*>(p.in.x) + elem / 2, false);
-            e_in[k] = __float_as_uint(load_input_scale(p.in, static_cast<uint32_t>(row0 + r), static_cast<uint32_t>(col0 + c16 * 16))) >> 23;
-            atomicMax(&exp_max[(r / p.out_bm) * ncb + cb], static_cast<int>(e_in[k]));
+        const uint32_t r = row0 + 32 * k;
+        if (kFull || (col_ok && r < static_cast<uint32_t>(p.in.num_tokens))) {
+            cp_async_16(&st.codes[k][t], src + k * pitch);
+            cp_async_4(&st.scale_word[0][k][t], input_scale_word(p.in, r, col));
+            if (two_scales) cp_async_4(&st.scale_word[1][k][t], input_scale_word(p.in, r, col + 16));
+        } else {
+            st.codes[k][t] = make_uint4(0u, 0u, 0u, 0u);
+            st.scale_word[0][k][t] = 0u;
+            st.scale_word[1][k][t] = 0u;
+        }
+    }
+}
+
+// The thread's pieces of a tile whose copies have landed.
+__device__ __forceinline__ void lossless_fetch(const LosslessParams& p, const LosslessStage& st, uint32_t tile_k, int t, int c32, LosslessPieces& q) {
+    const uint32_t col = tile_k * kLosslessCols + c32 * 32;
+    const bool ue8m0 = p.in.in_sf_flags & TKQ_SF_UE8M0;
+    const bool two_scales = p.in.in_block_k == 16;
+    const uint32_t k0 = p.in.in_shift_k1 ? col >> (p.in.in_shift_k1 - 1) : col / p.in.in_block_k;
+    const uint32_t shift0 = ue8m0 ? 8u * (k0 & 3u) : 23u, shift1 = ue8m0 ? 8u * ((k0 + 1u) & 3u) : 23u;
+    const uint32_t mask = ue8m0 ? 0xFFu : 0x1FFu;  // scales are positive: bit 8 of the shifted fp32 word is its sign, zero
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        q.codes[i] = st.codes[i][t];
+        q.e_in[i][0] = (st.scale_word[0][i][t] >> shift0) & mask;
+        q.e_in[i][1] = two_scales ? (st.scale_word[1][i][t] >> shift1) & mask : q.e_in[i][0];
+    }
+}
+
+// 8 FP4 codes (one word, even index in the low nibble) times a power of two (the same f16 in both halves of
+// `rel`) -> 8 e4m3 bytes.  The arithmetic stays in f16: a product is exact there (an FP4 value has one mantissa bit
+// and rel >= 2^-14), so rounding it to e4m3 gives what the fp32 route of the other casts gives, in 3 instead of 5
+// instructions per pair.
+__device__ __forceinline__ void fp4x8_times_pow2_to_e4m3(uint32_t word, uint32_t rel, uint32_t& out0, uint32_t& out1) {
+    asm("{ .reg .b8 b0, b1, b2, b3; .reg .b16 c0, c1, c2, c3; .reg .b32 h0, h1, h2, h3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 h0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 h1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 h2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 h3, b3;\n\t"
+        "mul.rn.f16x2 h0, h0, %3;\n\t"
+        "mul.rn.f16x2 h1, h1, %3;\n\t"
+        "mul.rn.f16x2 h2, h2, %3;\n\t"
+        "mul.rn.f16x2 h3, h3, %3;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 c0, h0;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 c1, h1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 c2, h2;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f16x2 c3, h3;\n\t"
+        "mov.b32 %0, {c0, c1};\n\t"
+        "mov.b32 %1, {c2, c3}; }"
+        : "=r"(out0), "=r"(out1)
+        : "r"(word), "r"(rel));
+}
+
+// 2^(e_in - e_out) as f16 in both halves of a word; counts the pieces the reference would assert on (e_in + 5 >= e_out,
+// exact representability).  The difference is at most 6 (the block's maximum covers e_in); below 2^-14 every product is
+// less than half of e4m3's smallest step and rounds to zero.
+__device__ __forceinline__ uint32_t lossless_rel(uint32_t e_in, int e_out) {
+    const int d = static_cast<int>(e_in) - e_out;
+    if (d < -5) atomicAdd(&g_lossless_range_violations, 1u);
+    const uint32_t h = d >= -14 ? static_cast<uint32_t>(d + 15) << 10 : 0u;
+    return h | (h << 16);
+}
+
+// One tile: exponent maxima per output block (first over the lanes of the warp that hold pieces of the same block -- a
+// warp is 4 rows x 8 pieces and its rows lie in one 32-row band -- then one shared-memory atomic per warp and block;
+// one atomic per piece is a thousand atomics on a single word for 128 x 128 blocks), the block's barrier, scales, codes.
+template <int OBM, int OBK, bool kFull>
+__device__ __forceinline__ void lossless_tile(const LosslessParams& p, const LosslessPieces& cur, uint32_t tile_m, uint32_t tile_k, int* emax,
+                                              int* emax_next, int t, int c32, int r_base) {
+    constexpr int NRB = kTile / OBM, NCB = kLosslessCols / OBK;
+    const uint32_t hidden = static_cast<uint32_t>(p.in.hidden);
+    const uint32_t row0 = tile_m * kTile, col0 = tile_k * kLosslessCols;
+    const int valid_rows = kFull ? kTile : static_cast<int>(min(static_cast<uint32_t>(p.in.num_tokens) - row0, static_cast<uint32_t>(kTile)));
+    const int valid_cols = kFull ? kLosslessCols : static_cast<int>(min(hidden - col0, static_cast<uint32_t>(kLosslessCols)));
+    const int cb = c32 * 32 / OBK;
+    for (int i = t; i < NRB * NCB; i += kTileThreads) emax_next[i] = 0;
+
+    int m[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m[k] = static_cast<int>(max(cur.e_in[k][0], cur.e_in[k][1]));
+    if constexpr (OBM == kTile) m[0] = max(max(m[0], m[1]), max(m[2], m[3]));
+#pragma unroll
+    for (int k = 0; k < (OBM == kTile ? 1 : 4); ++k) {
+        if (OBK == 128) {
+            m[k] = max(m[k], __shfl_xor_sync(kFullMask, m[k], 1));
+            m[k] = max(m[k], __shfl_xor_sync(kFullMask, m[k], 2));
+        }
+        if (OBM >= 32) {
+            m[k] = max(m[k], __shfl_xor_sync(kFullMask, m[k], 8));
+            m[k] = max(m[k], __shfl_xor_sync(kFullMask, m[k], 16));
+        }
+    }
+    if ((OBK == 32 || (c32 & 3) == 0) && (OBM < 32 || (t & 31) < 8)) {
+        if constexpr (OBM == kTile) {
+            atomicMax(&emax[cb], m[0]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) atomicMax(&emax[((r_base + 32 * k) / OBM) * NCB + cb], m[k]);
         }
     }
     __syncthreads();
-    const int64_t num_kb = (hidden + p.out_bk - 1) / p.out_bk;
-    for (int i = t; i < nrb * ncb; i += kTileThreads) {
-        const int rb = i / ncb, kb = i % ncb;
-        if (rb * static_cast<int>(p.out_bm) < valid_rows && kb * static_cast<int>(p.out_bk) < valid_cols) {
-            const uint32_t e = exp_max[i] >= 6 ? exp_max[i] - 6 : 0;
-            const int64_t m_idx = tile_m * nrb + rb, k_idx = tile_k * ncb + kb;
-            if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_byte(p.sf, p.sf_stride, m_idx, static_cast<uint32_t>(k_idx), static_cast<uint32_t>(num_kb), e);
+    for (int i = t; i < NRB * NCB; i += kTileThreads) {
+        const int rb = i / NCB, kb = i % NCB;
+        if (rb * OBM < valid_rows && kb * OBK < valid_cols) {
+            const uint32_t e = emax[i] >= 6 ? emax[i] - 6 : 0;
+            const int64_t m_idx = static_cast<int64_t>(tile_m) * NRB + rb;
+            const uint32_t k_idx = tile_k * NCB + kb;
+            if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_byte(p.sf, p.sf_stride, m_idx, k_idx, (hidden + OBK - 1) / OBK, e);
             else store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, m_idx, k_idx, __uint_as_float(e << 23));
         }
     }
+    if (!kFull && c32 * 32 >= valid_cols) return;  // after the tile's only barrier
+    uint8_t* dst = p.in.out + (static_cast<int64_t>(row0 + r_base) * hidden + col0 + c32 * 32);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int r = r_base + 32 * k;
-        if (col_ok && r < valid_rows) {
-            const int m = exp_max[(r / p.out_bm) * ncb + cb];
-            const uint32_t e_out = m >= 6 ? m - 6 : 0;
-            // where the reference asserts on the device (e_in + 5 >= e_out, exact representability), count and carry on
-            if (e_in[k] + 5u < e_out) atomicAdd(&g_lossless_range_violations, 1u);
-            const float rel = e_in[k] + 127u > e_out ? __uint_as_float((e_in[k] - e_out + 127u) << 23) : 0.0f;  // 2^(e_in - e_out)
-            float v[16];
-            QuantSource<TKQ_FMT_E2M1>::unpack(raw[k], v, rel);
-            stg128(p.in.out + (row0 + r) * hidden + col0 + c16 * 16, cvt_e4m3x4(v[0], v[1], v[2], v[3]), cvt_e4m3x4(v[4], v[5], v[6], v[7]),
-                   cvt_e4m3x4(v[8], v[9], v[10], v[11]), cvt_e4m3x4(v[12], v[13], v[14], v[15]));
+        if (kFull || r < valid_rows) {
+            const int mx = emax[(r / OBM) * NCB + cb];
+            const int e_out = mx >= 6 ? mx - 6 : 0;
+            const uint32_t rel0 = lossless_rel(cur.e_in[k][0], e_out), rel1 = lossless_rel(cur.e_in[k][1], e_out);
+            uint32_t w[8];
+            fp4x8_times_pow2_to_e4m3(cur.codes[k].x, rel0, w[0], w[1]);
+            fp4x8_times_pow2_to_e4m3(cur.codes[k].y, rel0, w[2], w[3]);
+            fp4x8_times_pow2_to_e4m3(cur.codes[k].z, rel1, w[4], w[5]);
+            fp4x8_times_pow2_to_e4m3(cur.codes[k].w, rel1, w[6], w[7]);
+            uint8_t* d = dst + static_cast<uint32_t>(k) * 32u * hidden;
+            if (p.wide_stores) {
+                stg256(d, w);
+            } else {
+                stg128(d, w[0], w[1], w[2], w[3]);
+                stg128(d + 16, w[4], w[5], w[6], w[7]);
+            }
         }
     }
+}
+
+// Persistent blocks: block b takes tiles b, b + grid, ...; the copies of the tiles kLosslessDepth ahead are issued
+// before the current one is reduced and stored.  The exponent maxima rotate over three buffers: the one for the next
+// tile is cleared before this tile's barrier, when nobody reads it.  OBM x OBK is the output block (1 | 32 | 128) x (32 | 128).
+template <int OBM, int OBK>
+__global__ void __launch_bounds__(kTileThreads, kLosslessBlocksPerSm) per_block_cast_lossless_kernel(const LosslessParams p, const uint32_t num_tiles) {
+    constexpr int NRB = kTile / OBM, NCB = kLosslessCols / OBK;
+    constexpr int kStages = kLosslessDepth + 1;
+    extern __shared__ __align__(16) uint8_t lossless_smem[];
+    LosslessStage* const stages = reinterpret_cast<LosslessStage*>(lossless_smem);
+    __shared__ int exp_max[3][NRB * NCB];
+    const int t = threadIdx.x;
+    const int c32 = t & 7, r_base = t >> 3;
+    const uint32_t full_m = static_cast<uint32_t>(p.in.num_tokens) / kTile, full_k = static_cast<uint32_t>(p.in.hidden) / kLosslessCols;
+    const uint32_t step_m = gridDim.x / p.tiles_k, step_k = gridDim.x - step_m * p.tiles_k;
+    for (int i = t; i < NRB * NCB; i += kTileThreads) exp_max[0][i] = 0;
+    __syncthreads();
+
+    // (tile_m, tile_k) of the tile being processed and of the one being copied advance by the grid size without divisions
+    auto advance = [&](uint32_t& m, uint32_t& k) {
+        m += step_m;
+        k += step_k;
+        if (k >= p.tiles_k) {
+            k -= p.tiles_k;
+            ++m;
+        }
+    };
+    auto issue = [&](uint32_t tile, uint32_t m, uint32_t k, uint32_t stage) {  // one group per tile slot, empty past the end
+        if (tile < num_tiles) {
+            if (m < full_m && k < full_k) lossless_issue<true>(p, m, k, t, c32, r_base, stages[stage]);
+            else lossless_issue<false>(p, m, k, t, c32, r_base, stages[stage]);
+        }
+        cp_async_commit();
+    };
+    uint32_t tile = blockIdx.x;
+    uint32_t cur_m = tile / p.tiles_k, cur_k = tile - cur_m * p.tiles_k;
+    uint32_t nxt_tile = tile, nxt_m = cur_m, nxt_k = cur_k, nxt_stage = 0;
+#pragma unroll
+    for (int d = 0; d < kLosslessDepth; ++d) {
+        issue(nxt_tile, nxt_m, nxt_k, nxt_stage);
+        nxt_tile += gridDim.x;
+        advance(nxt_m, nxt_k);
+        ++nxt_stage;
+    }
+    uint32_t stage = 0, buf = 0;
+    for (; tile < num_tiles; tile += gridDim.x) {
+        issue(nxt_tile, nxt_m, nxt_k, nxt_stage);  // into the stage this thread emptied in the previous iteration
+        nxt_tile += gridDim.x;
+        advance(nxt_m, nxt_k);
+        nxt_stage = nxt_stage == kStages - 1 ? 0 : nxt_stage + 1;
+        cp_async_wait<kLosslessDepth>();
+        LosslessPieces cur;
+        lossless_fetch(p, stages[stage], cur_k, t, c32, cur);
+        int* const a = exp_max[buf];
+        buf = buf == 2 ? 0 : buf + 1;
+        if (cur_m < full_m && cur_k < full_k) lossless_tile<OBM, OBK, true>(p, cur, cur_m, cur_k, a, exp_max[buf], t, c32, r_base);
+        else lossless_tile<OBM, OBK, false>(p, cur, cur_m, cur_k, a, exp_max[buf], t, c32, r_base);
+        advance(cur_m, cur_k);
+        stage = stage == kStages - 1 ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
@@ -1317,9 +1516,10 @@ extern "C" int tkq_per_block_cast_lossless(const void* x, const void* x_sf, unsi
     if (!bm_ok || !bk_ok || out_block_m % x_block_m != 0 || out_block_k % x_block_k != 0 || x_block_k % 16 != 0 || hidden % 32 != 0)
         return set_error(TKQ_E_UNSUPPORTED,
                          "per_block_cast_lossless: output blocks (1|32|128) x (32|128), multiples of the input block; hidden % 32 == 0");
-    if (reinterpret_cast<uintptr_t>(x) % 8 != 0 || (x_row_stride / 2) % 8 != 0 || !aligned16(out) ||
-        (reinterpret_cast<uintptr_t>(sf) & 3u) || (reinterpret_cast<uintptr_t>(x_sf) & 3u) || ((flags & TKQ_SF_UE8M0) && (sf_stride & 3)))
-        return set_error(TKQ_E_ALIGNMENT, "per_block_cast_lossless: x rows 8-byte aligned, out 16-byte aligned, scales 4-byte aligned");
+    if (!aligned16(x) || (x_row_stride / 2) % 16 != 0 || !aligned16(out) ||
+        (reinterpret_cast<uintptr_t>(sf) & 3u) || (reinterpret_cast<uintptr_t>(x_sf) & 3u) || ((flags & TKQ_SF_UE8M0) && (sf_stride & 3)) ||
+        ((x_sf_flags & TKQ_SF_UE8M0) && (x_sf_stride & 3)))
+        return set_error(TKQ_E_ALIGNMENT, "per_block_cast_lossless: x rows and out 16-byte aligned, scales 4-byte aligned");
     LosslessParams p{};
     p.in.x = x;
     p.in.out = static_cast<uint8_t*>(out);
@@ -1334,12 +1534,33 @@ extern "C" int tkq_per_block_cast_lossless(const void* x, const void* x_sf, unsi
     set_input_block_shifts(p.in);
     p.sf = sf;
     p.sf_stride = sf_stride;
-    p.out_bm = static_cast<uint32_t>(out_block_m);
-    p.out_bk = static_cast<uint32_t>(out_block_k);
-    p.tiles_k = static_cast<uint32_t>((hidden + kTile - 1) / kTile);
+    p.tiles_k = static_cast<uint32_t>((hidden + kLosslessCols - 1) / kLosslessCols);
     p.flags = flags;
+    p.wide_stores = reinterpret_cast<uintptr_t>(out) % 32 == 0;
     const int64_t tiles = ((num_tokens + kTile - 1) / kTile) * p.tiles_k;
-    if (tiles >= (int64_t{1} << 31)) return set_error(TKQ_E_UNSUPPORTED, "too many tiles; split the token dimension");
-    per_block_cast_lossless_kernel<<<static_cast<unsigned>(tiles), kTileThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    if (tiles >= (int64_t{1} << 31) || num_tokens >= (int64_t{1} << 31) || x_row_stride >= (int64_t{1} << 24))
+        return set_error(TKQ_E_UNSUPPORTED, "per_block_cast_lossless: more than 2^31 tokens or tiles, or rows of more than 2^24 values");
+    const int sms = device_sm_count();
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t n = static_cast<uint32_t>(tiles);
+    auto launch = [&](auto kernel) -> int {
+        constexpr int kSmem = (kLosslessDepth + 1) * static_cast<int>(sizeof(LosslessStage));
+        if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmem)) return rc;
+        const int per_sm = std::min(kLosslessBlocksPerSm, cached_occupancy(reinterpret_cast<const void*>(kernel), kTileThreads, kSmem));
+        const int grid = static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sms) * std::max(per_sm, 1)));
+        kernel<<<grid, kTileThreads, kSmem, st>>>(p, n);
+        return 0;
+    };
+    int rc = 0;
+    if (out_block_k == 128) {
+        if (out_block_m == 128) rc = launch(per_block_cast_lossless_kernel<128, 128>);
+        else if (out_block_m == 32) rc = launch(per_block_cast_lossless_kernel<32, 128>);
+        else rc = launch(per_block_cast_lossless_kernel<1, 128>);
+    } else {
+        if (out_block_m == 128) rc = launch(per_block_cast_lossless_kernel<128, 32>);
+        else if (out_block_m == 32) rc = launch(per_block_cast_lossless_kernel<32, 32>);
+        else rc = launch(per_block_cast_lossless_kernel<1, 32>);
+    }
+    if (rc) return rc;
     return check_launch("per_block_cast_lossless");
 }
