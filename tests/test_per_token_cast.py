@@ -118,6 +118,31 @@ def test_misaligned_view_uses_narrow_loads(oracle, cuda_device):
     assert_equal(to_host(sf), sf_ref)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize('xb', [(128, 128), (32, 32)], ids=lambda b: f'b{b[0]}')
+def test_requantising_cast_of_tiny_codes(oracle, cuda_device, xb):
+    """The f16 route of the production re-quantising cast (e4m3 + ue8m0 in, e4m3 g128 + ue8m0 out, hidden % 1024 == 0)
+    at its edges: one large value per input block leaves the other groups of the block with subnormal codes only, so
+    that 2^(e_in - e_out) exceeds f16's range and those pieces take the fp32 route; rows of zeros; a block of zeros."""
+    from tilekernels_b200 import quant
+    kw = dict(use_tma_aligned_col_major_sf=True, round_sf=True, use_packed_ue8m0=True)
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn((384, 2048), generator=g) * 2.0 ** -8.5
+    x[::xb[0], ::xb[1]] = 400.0          # one large value per input block
+    x[5] = 0                             # a row of zeros next to it
+    x[128:256, 1024:1152] = 0            # a whole 128 x 128 block of zeros
+    x[300:, :] *= 2.0 ** 9               # ordinary magnitudes in the last rows
+    x_cpu = x.to(torch.bfloat16)
+    q_ref, qsf_ref = oracle.cast(x_cpu, 'e4m3', xb, **kw)
+    q, qsf = quant.per_block_cast(x_cpu.to(cuda_device), 'e4m3', xb, **kw)
+    assert_equal(to_host(q), q_ref)
+    out, sf = quant.per_token_cast((q, qsf), 'e4m3', 128, x_block_size=xb, **kw)
+    out_ref, sf_ref = oracle.cast((q_ref, qsf_ref), 'e4m3', (1, 128), x_block_size=xb, **kw)
+    assert_equal(to_host(sf), sf_ref)
+    assert_equal(to_host(out), out_ref)
+    assert (to_host(out).view(torch.uint8) & 0x7F).max() > 0x40  # the tiny groups were scaled up, not flushed
+
+
 def _requant_params():
     for num_tokens, hidden in ((4001, 576), (4001, 7168), (129, 2048), (33, 4096), (65, 1536)):
         for in_fmt in ('e4m3', 'e2m1'):

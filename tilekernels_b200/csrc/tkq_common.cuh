@@ -151,6 +151,13 @@ __device__ __forceinline__ float max3_abs(float a, float b, float c) {
     return d;
 }
 
+// max of two pairs of unsigned 16-bit values; non-negative bf16 or f16 numbers order like their bit patterns
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 // Where a scale goes (reference: tile_kernels/quant/common.py:238-244 store_sf).
 // m = token-block index, k = channel-block index.
 __device__ __forceinline__ void store_sf_f32(void* sf, int64_t sf_stride, bool col_major, int64_t m, int64_t k,

@@ -113,8 +113,16 @@ static int dispatch_quant_group(const TokenCastParams& p, int64_t g, cudaStream_
         case 128:
             // the production flag set: compile-time flags, and two 512-value steps per warp so that a lane has 32 bytes
             // of FP8 input in flight as the bf16 casts have (B200, [32768, 7168] from 128x128 blocks: 101 us generic,
-            // 93 us with the flags fixed, 88 us with two steps, 90 us with four)
+            // 93 us with the flags fixed, 88 us with two steps, 90 us with four).  FP8 in and out with ue8m0 scales on both
+            // sides has a kernel of its own (f16 arithmetic, 32 values per lane): 79 us
             if (lean_flags(p)) {
+                if constexpr (QFMT == TKQ_FMT_E4M3 && FMT == TKQ_FMT_E4M3) {
+                    const bool rows32 = reinterpret_cast<uintptr_t>(p.x) % 32 == 0 && p.x_stride % 32 == 0 && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 &&
+                                        p.out_stride % 32 == 0;
+                    // launch_group_kernel counts 512-value steps: two of them per 1024-value step of this kernel
+                    if ((p.in_sf_flags & TKQ_SF_UE8M0) && p.in_block_k % 32 == 0 && p.hidden % 1024 == 0 && rows32)
+                        return launch_group_kernel(requant_pow2_kernel<1>, p, 2, 0, stream, what);
+                }
                 if (p.hidden >= 1024) return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 8, 2, 0, true>, p, 2, 0, stream, what);
                 return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 8, 1, 0, true>, p, 1, 0, stream, what);
             }

@@ -333,13 +333,6 @@ __global__ void __launch_bounds__(kTileThreads, 5) per_block_cast_direct_kernel(
     }
 }
 
-// max of two pairs of unsigned 16-bit values; non-negative bf16 numbers order like their bit patterns
-__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-
 // ---------------------------------------------------------------------------
 // The per-channel cast (128 tokens x 1 channel) of bf16 input straight from global memory, same thread mapping as the
 // direct per-block cast.  Column maxima stay packed (two |bf16| per word, compared as unsigned 16-bit integers):
