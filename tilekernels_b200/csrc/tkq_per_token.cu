@@ -111,18 +111,21 @@ static int dispatch_quant_group(const TokenCastParams& p, int64_t g, cudaStream_
         case 32: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 2, 1, 0>, p, 1, 0, stream, what);
         case 64: return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 4, 1, 0>, p, 1, 0, stream, what);
         case 128:
-            // the production flag set: compile-time flags, and two 512-value steps per warp so that a lane has 32 bytes
-            // of FP8 input in flight as the bf16 casts have (B200, [32768, 7168] from 128x128 blocks: 101 us generic,
-            // 93 us with the flags fixed, 88 us with two steps, 90 us with four).  FP8 in and out with ue8m0 scales on both
-            // sides has a kernel of its own (f16 arithmetic, 32 values per lane): 79 us
-            if (lean_flags(p)) {
-                if constexpr (QFMT == TKQ_FMT_E4M3 && FMT == TKQ_FMT_E4M3) {
-                    const bool rows32 = reinterpret_cast<uintptr_t>(p.x) % 32 == 0 && p.x_stride % 32 == 0 && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 &&
-                                        p.out_stride % 32 == 0;
-                    // launch_group_kernel counts 512-value steps: two of them per 1024-value step of this kernel
-                    if ((p.in_sf_flags & TKQ_SF_UE8M0) && p.in_block_k % 32 == 0 && p.hidden % 1024 == 0 && rows32)
-                        return launch_group_kernel(requant_pow2_kernel<1>, p, 2, 0, stream, what);
+            // To e4m3, rows of whole 1024-value steps on 32-byte boundaries, input blocks at least 32 wide: the kernel with
+            // 32 values per lane, in f16 arithmetic when both sides' scales are powers of two.  B200, FP8 [32768, 7168]
+            // from 128x128 ue8m0 blocks: 101 us general kernel, 93 us with the flags fixed at compile time, 88 us with
+            // two steps per warp, 79 us with this one.
+            if constexpr (FMT == TKQ_FMT_E4M3) {
+                const int64_t in_row_bytes = QFMT == TKQ_FMT_E4M3 ? p.x_stride : p.x_stride / 2;
+                const bool rows32 = reinterpret_cast<uintptr_t>(p.x) % 32 == 0 && in_row_bytes % 32 == 0 && reinterpret_cast<uintptr_t>(p.out) % 32 == 0 &&
+                                    p.out_stride % 32 == 0;
+                if (!(p.flags & (TKQ_SF_ONLY | TKQ_CAST_ONLY)) && p.in_block_k % 32 == 0 && p.hidden % 1024 == 0 && rows32) {
+                    // launch_group_kernel counts 512-value steps: two of them per step of this kernel
+                    if ((p.in_sf_flags & TKQ_SF_UE8M0) && p.fast_pow2) return launch_group_kernel(requant32_kernel<QFMT, true>, p, 2, 0, stream, what);
+                    return launch_group_kernel(requant32_kernel<QFMT, false>, p, 2, 0, stream, what);
                 }
+            }
+            if (lean_flags(p)) {
                 if (p.hidden >= 1024) return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 8, 2, 0, true>, p, 2, 0, stream, what);
                 return launch_group_kernel(group_cast_kernel<QuantSource<QFMT>, kSourceQuant, FMT, 8, 1, 0, true>, p, 1, 0, stream, what);
             }

@@ -184,26 +184,31 @@ __global__ void __launch_bounds__(kGroupThreads) group_cast_kernel(const TokenCa
 }
 
 // ---------------------------------------------------------------------------
-// The re-quantising cast in its production form: e4m3 codes with packed ue8m0 block scales in, e4m3 with one packed
-// ue8m0 scale per 128 values out, rows of whole 1024-value steps, 32-byte aligned rows.  A lane owns 32 consecutive
-// values (one 256-bit load, one 256-bit store: whole sectors both ways), a group is four lanes.  With powers of two on
-// both sides an output value is the input value times 2^(e_in - e_out), which is exact in f16 (four significant bits,
-// magnitude at most 448; what falls below f16's 2^-24 grid is far below half of e4m3's smallest step and rounds to zero
-// either way), so the codes go e4m3x2 -> f16x2 -> one multiplication -> e4m3x2 without a detour through fp32, and the
-// maximum is taken over the f16 magnitudes and scaled once per lane.  Same bits as group_cast_kernel<QuantSource<e4m3>,
-// ...>; 2^(e_in - e_out) above f16's range (a group of nothing but tiny subnormal codes) sends the lane's values
-// through fp32.
+// The re-quantising cast to e4m3 with one scale per 128 values, for rows of whole 1024-value steps on 32-byte
+// boundaries and input blocks at least 32 wide.  A lane owns 32 consecutive values (one 256-bit load of FP8 or one
+// 128-bit load of FP4, one 256-bit store: whole sectors), a group is four lanes.  The codes are widened to f16, which
+// holds every e4m3 and e2m1 value; the group maximum is the largest f16 magnitude times the lane's input scale,
+// rounded once (x -> fl(x * s) is monotone, so this is the maximum of the products the general kernel forms).
+//   kPow2 (input scales ue8m0, output scales powers of two): an output value is the input value times
+//     2^(e_in - e_out), exact in f16 (at most four significant bits, magnitude at most 448; what falls below f16's
+//     2^-24 grid is far below half of e4m3's smallest step and rounds to zero either way), so the codes go
+//     f16x2 -> one multiplication -> e4m3x2 and never become fp32.  2^(e_in - e_out) above f16's range (a group of
+//     nothing but tiny codes) sends the lane's values through fp32.
+//   otherwise: value * input scale * inverse output scale in fp32, rounded after each product as in the general kernel.
+// Same bits as group_cast_kernel<QuantSource<QFMT>, ..., e4m3, 8, ...>.
 // ---------------------------------------------------------------------------
-template <int U>  // 1024-value steps per item
-__global__ void __launch_bounds__(kGroupThreads) requant_pow2_kernel(const TokenCastParams p) {
+template <int QFMT, bool kPow2>
+__global__ void __launch_bounds__(kGroupThreads) requant32_kernel(const TokenCastParams p) {
+    constexpr int kWords = QFMT == TKQ_FMT_E4M3 ? 8 : 4;  // 32 codes
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
+    const bool round_sf = p.flags & TKQ_ROUND_SF;
     const uint8_t* xb = static_cast<const uint8_t*>(p.x);
     uint32_t row = warp / p.items_per_row;
     uint32_t sub = warp - row * p.items_per_row;
     for (uint32_t item = warp; item < p.total_items; item += nwarps) {
-        const uint32_t col0 = sub * (1024u * U) + lane * 32u;
+        const uint32_t col = sub * 1024u + lane * 32u;
         const uint32_t this_row = row;
         sub += p.stride_items;
         row += p.stride_rows;
@@ -211,18 +216,21 @@ __global__ void __launch_bounds__(kGroupThreads) requant_pow2_kernel(const Token
             sub -= p.items_per_row;
             ++row;
         }
-        const uint8_t* src = xb + static_cast<int64_t>(this_row) * p.x_stride + col0;
-        U32x8 raw[U];
-        uint32_t e_in[U];
+        const uint8_t* src = xb + (static_cast<int64_t>(this_row) * p.x_stride + col) * kWords / 8;
+        uint32_t raw[kWords];
+        if constexpr (QFMT == TKQ_FMT_E4M3) {
+            const U32x8 r = ldg256(src);
 #pragma unroll
-        for (int u = 0; u < U; ++u) raw[u] = ldg256(src + u * 1024);
+            for (int i = 0; i < 8; ++i) raw[i] = r.v[i];
+        } else {
+            const U32x4 r = ldg128(src);
 #pragma unroll
-        for (int u = 0; u < U; ++u) e_in[u] = __float_as_uint(load_input_scale(p, this_row, col0 + u * 1024u)) >> 23;
-        uint8_t* out_row = p.out + static_cast<int64_t>(this_row) * p.out_stride;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint32_t col = col0 + u * 1024u;
-            uint32_t h[16];
+            for (int i = 0; i < 4; ++i) raw[i] = r.v[i];
+        }
+        const float s_in = load_input_scale(p, this_row, col);
+        uint8_t* dst = p.out + static_cast<int64_t>(this_row) * p.out_stride + col;
+        uint32_t h[16];  // the 32 values as f16 pairs
+        if constexpr (QFMT == TKQ_FMT_E4M3) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 asm("{ .reg .b16 lo, hi;\n\t"
@@ -230,36 +238,48 @@ __global__ void __launch_bounds__(kGroupThreads) requant_pow2_kernel(const Token
                     "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
                     "cvt.rn.f16x2.e4m3x2 %1, hi; }"
                     : "=r"(h[2 * i]), "=r"(h[2 * i + 1])
-                    : "r"(raw[u].v[i]));
+                    : "r"(raw[i]));
             }
-            // largest magnitude of the lane: non-negative f16 values order like their bit patterns
-            uint32_t m2 = h[0] & 0x7FFF7FFFu;
+        } else {
 #pragma unroll
-            for (int i = 1; i < 16; ++i) m2 = max_u16x2(m2, h[i] & 0x7FFF7FFFu);
-            const uint32_t m1 = max(m2 & 0xFFFFu, m2 >> 16);
-            float amax = __fmul_rn(__half2float(__ushort_as_half(static_cast<unsigned short>(m1))), __uint_as_float(e_in[u] << 23));
-            amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 2));
-            const Scale s = make_scale_pow2<TKQ_FMT_E4M3>(amax, p.clamp_min);
-            if ((lane & 3u) == 0) store_sf_ue8m0_byte(p.sf, p.sf_stride, this_row, col >> 7, p.num_groups, s.e8);
-            const int d = static_cast<int>(e_in[u]) - static_cast<int>(s.e8);
-            if (d > 15 && m1 != 0u) {  // 2^d is not an f16: these values through fp32, as the general kernel does it
-                QuantSource<TKQ_FMT_E4M3>::Raw r;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    float v[16];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) r.a.v[i] = raw[u].v[4 * q + i];
-                    QuantSource<TKQ_FMT_E4M3>::unpack(r, v, __uint_as_float(e_in[u] << 23));
-                    quantize_store_e4m3x16(v, s.inv, out_row + col + 16 * q);
-                }
-                continue;
+            for (int i = 0; i < 4; ++i) {
+                asm("{ .reg .b8 b0, b1, b2, b3;\n\t"
+                    "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+                    "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+                    "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+                    "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+                    "cvt.rn.f16x2.e2m1x2 %3, b3; }"
+                    : "=r"(h[4 * i]), "=r"(h[4 * i + 1]), "=r"(h[4 * i + 2]), "=r"(h[4 * i + 3])
+                    : "r"(raw[i]));
             }
+        }
+        // largest magnitude of the lane: non-negative f16 values order like their bit patterns
+        uint32_t m2 = h[0] & 0x7FFF7FFFu;
+#pragma unroll
+        for (int i = 1; i < 16; ++i) m2 = max_u16x2(m2, h[i] & 0x7FFF7FFFu);
+        const uint32_t m1 = max(m2 & 0xFFFFu, m2 >> 16);
+        float amax = __fmul_rn(__half2float(__ushort_as_half(static_cast<unsigned short>(m1))), s_in);
+        amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(kFullMask, amax, 2));
+        const Scale s = kPow2 ? make_scale_pow2<TKQ_FMT_E4M3>(amax, p.clamp_min) : make_scale_for<TKQ_FMT_E4M3>(amax, p.clamp_min, round_sf, p.fast_pow2);
+        if ((lane & 3u) == 0) {
+            const uint32_t g = col >> 7;
+            if (p.flags & TKQ_SF_UE8M0) store_sf_ue8m0_byte(p.sf, p.sf_stride, this_row, g, p.num_groups, s.e8);
+            else store_sf_f32(p.sf, p.sf_stride, p.flags & TKQ_SF_COL_MAJOR, this_row, g, s.sf);
+        }
+        uint32_t w[8];
+        bool through_f16 = kPow2;
+        uint32_t rel = 0;
+        if constexpr (kPow2) {
+            const uint32_t e_in = __float_as_uint(s_in) >> 23;
+            const int d = static_cast<int>(e_in) - static_cast<int>(s.e8);
+            through_f16 = d <= 15 || m1 == 0u;
             // 2^d as f16 in both halves: normal from 2^-14, subnormal down to 2^-24, zero below (and for a zero input scale)
-            uint32_t rel = d >= -14 ? static_cast<uint32_t>(min(d, 15) + 15) << 10 : (d >= -24 ? 1u << (d + 24) : 0u);
-            if (e_in[u] == 0u) rel = 0u;
+            rel = d >= -14 ? static_cast<uint32_t>(min(d, 15) + 15) << 10 : (d >= -24 ? 1u << (d + 24) : 0u);
+            if (e_in == 0u) rel = 0u;
             rel |= rel << 16;
-            uint32_t w[8];
+        }
+        if (through_f16) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 asm("{ .reg .b16 c0, c1; .reg .b32 a, b;\n\t"
@@ -271,8 +291,15 @@ __global__ void __launch_bounds__(kGroupThreads) requant_pow2_kernel(const Token
                     : "=r"(w[i])
                     : "r"(h[2 * i]), "r"(h[2 * i + 1]), "r"(rel));
             }
-            stg256(out_row + col, w);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 a = mul2(mul2(__half22float2(*reinterpret_cast<const __half2*>(&h[2 * i])), splat2(s_in)), splat2(s.inv));
+                const float2 b = mul2(mul2(__half22float2(*reinterpret_cast<const __half2*>(&h[2 * i + 1])), splat2(s_in)), splat2(s.inv));
+                w[i] = cvt_e4m3x4(a.x, a.y, b.x, b.y);
+            }
         }
+        stg256(dst, w);
     }
 }
 
