@@ -209,3 +209,61 @@ def test_cast_back_guard_bands(oracle, cuda_device, num_tokens, hidden, out_dtyp
     assert rc == 0, _lib.lib().tkq_last_error_string()
     torch.cuda.synchronize()
     out.check(_raw(want), 'cast_back data')
+
+
+def _device_sf(sf_ref: torch.Tensor, nm: int, nk: int, col: bool, ue: bool, device):
+    """An input scale tensor in device storage laid out as the C ABI reads it; returns (tensor, sf_stride argument)."""
+    store = _expected_sf(sf_ref, nm, nk, col, ue)
+    return store.to(device), _sf_geometry(nm, nk, col, ue)[1]
+
+
+@pytest.mark.parametrize('flags', [(False, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('in_fmt,in_block', [('e4m3', (128, 128)), ('e4m3', (1, 128)), ('e2m1', (1, 32))], ids=lambda v: str(v).replace(' ', ''))
+@pytest.mark.parametrize('hidden', [576, 1024, 2048])
+@pytest.mark.parametrize('num_tokens', [1, 127, 129, 1031])
+def test_requantising_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, in_fmt, in_block, flags):
+    """tkq_per_token_cast_quantized to e4m3 with groups of 128: rows of whole 1024-value steps take the kernel with 32 values
+    per lane, the others the general one; the same scale layout on both sides."""
+    from tilekernels_b200 import _lib
+    col, rnd, ue = flags
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(31 + num_tokens + hidden)).to(torch.bfloat16)
+    kw = dict(round_sf=rnd, use_tma_aligned_col_major_sf=col, use_packed_ue8m0=ue)
+    q, qsf = oracle.cast(x, in_fmt, in_block, **kw)
+    out_ref, sf_ref = oracle.cast((q, qsf), 'e4m3', (1, 128), x_block_size=in_block, **kw)
+    nm_in, nk_in = _ceil_div(num_tokens, in_block[0]), _ceil_div(hidden, in_block[1])
+    in_sf, in_stride = _device_sf(qsf, nm_in, nk_in, col, ue, cuda_device)
+    nk = _ceil_div(hidden, 128)
+    sf_bytes, sf_stride = _sf_geometry(num_tokens, nk, col, ue)
+    out, sf = Guarded(num_tokens * hidden, cuda_device), Guarded(sf_bytes, cuda_device)
+    qd = q.to(cuda_device)
+    sf_flags = _flags(col, False, ue)
+    rc = _lib.lib().tkq_per_token_cast_quantized(qd.data_ptr(), 0 if in_fmt == 'e4m3' else 1, in_sf.data_ptr(), sf_flags, in_stride, in_block[0],
+                                                 in_block[1], num_tokens, hidden, hidden, 0, 128, _flags(col, rnd, ue), out.ptr, sf.ptr,
+                                                 sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'requantising cast data')
+    sf.check(_expected_sf(sf_ref, num_tokens, nk, col, ue), 'requantising cast scales')
+
+
+@pytest.mark.parametrize('flags', [(False, True, False), (True, True, False), (True, True, True)], ids=flags_id)
+@pytest.mark.parametrize('out_block', [(128, 128), (32, 32), (1, 128)], ids=lambda b: f'{b[0]}x{b[1]}')
+@pytest.mark.parametrize('hidden', [64, 576, 1280])
+@pytest.mark.parametrize('num_tokens', TOKENS)
+def test_lossless_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, out_block, flags):
+    """tkq_per_block_cast_lossless on ragged shapes (partial 128 x 256 tiles in both directions)."""
+    from tilekernels_b200 import _lib
+    col, _, ue = flags
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(37 + num_tokens + hidden)).to(torch.bfloat16)
+    q, qsf = oracle.cast(x, 'e2m1', (1, 32), round_sf=True)
+    out_ref, sf_ref = oracle.per_block_cast_lossless((q, qsf), (1, 32), out_block, col, ue)
+    nm, nk = _ceil_div(num_tokens, out_block[0]), _ceil_div(hidden, out_block[1])
+    sf_bytes, sf_stride = _sf_geometry(nm, nk, col, ue)
+    out, sf = Guarded(num_tokens * hidden, cuda_device), Guarded(sf_bytes, cuda_device)
+    qd, sd = q.to(cuda_device), qsf.contiguous().to(cuda_device)
+    rc = _lib.lib().tkq_per_block_cast_lossless(qd.data_ptr(), sd.data_ptr(), 0, hidden // 32, 1, 32, num_tokens, hidden, hidden, out_block[0],
+                                                out_block[1], _flags(col, False, ue), out.ptr, sf.ptr, sf_stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'lossless cast data')
+    sf.check(_expected_sf(sf_ref, nm, nk, col, ue), 'lossless cast scales')
