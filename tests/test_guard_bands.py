@@ -267,3 +267,83 @@ def test_lossless_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, out_
     torch.cuda.synchronize()
     out.check(_raw(out_ref), 'lossless cast data')
     sf.check(_expected_sf(sf_ref, nm, nk, col, ue), 'lossless cast scales')
+
+
+@pytest.mark.parametrize('col', [False, True], ids=['row-major', 'col-major'])
+@pytest.mark.parametrize('row_bytes', [48, 576, 2064])
+@pytest.mark.parametrize('num_tokens,num_topk,num_pad', [(1, 1, 3), (33, 2, 7), (257, 6, 41)])
+def test_expand_guard_bands(oracle, cuda_device, num_tokens, num_topk, num_pad, row_bytes, col):
+    """tkq_expand_to_fused with scale words: rows of a whole number of 16-byte pieces (not of 32), padded positions
+    cleared, nothing written behind the last expanded row or in the padding of the column-major scale buffer."""
+    from tilekernels_b200 import _lib
+    gen = torch.Generator().manual_seed(41 + num_tokens + row_bytes)
+    entries = num_tokens * num_topk
+    routed = torch.rand(entries, generator=gen) > 0.2
+    num_routed = int(routed.sum().item())
+    num_expanded = num_routed + num_pad
+    positions = torch.randperm(num_expanded, generator=gen)[:num_routed].to(torch.int32)
+    t2p = torch.full((entries,), -1, dtype=torch.int32)
+    t2p[routed] = positions
+    p2e = torch.full((num_expanded,), -1, dtype=torch.int32)
+    p2e[positions.long()] = 0
+    t2p = t2p.view(num_tokens, num_topk)
+    sf_words = 5
+    x = torch.randint(0, 256, (num_tokens, row_bytes), generator=gen, dtype=torch.int32).to(torch.uint8)
+    x_sf = torch.randint(1, 2 ** 31 - 1, (num_tokens, sf_words), generator=gen, dtype=torch.int64).to(torch.int32)
+    out_ref = oracle.expand_to_fused(x, t2p, p2e)
+    sf_rows = oracle.expand_to_fused(x_sf, t2p, p2e)            # [num_expanded, sf_words]
+    out = Guarded(num_expanded * row_bytes, cuda_device)
+    stride = _align(num_expanded, 4) if col else sf_words
+    sf = Guarded((sf_words * stride if col else num_expanded * sf_words) * 4, cuda_device)
+    want_sf = torch.full((sf.nbytes,), FILL, dtype=torch.uint8)
+    if col:
+        want_sf.view(torch.int32).view(sf_words, stride)[:, :num_expanded] = sf_rows.T
+    else:
+        want_sf.view(torch.int32).view(num_expanded, sf_words)[:] = sf_rows
+    xd, sd, td, pd = x.to(cuda_device), x_sf.to(cuda_device), t2p.to(cuda_device), p2e.to(cuda_device)
+    rc = _lib.lib().tkq_expand_to_fused(xd.data_ptr(), num_tokens, row_bytes, sd.data_ptr(), sf_words, td.data_ptr(), num_topk, pd.data_ptr(),
+                                        num_expanded, 2 if col else 0, out.ptr, sf.ptr, stride, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'expand data')
+    sf.check(want_sf, 'expand scales')
+
+
+@pytest.mark.parametrize('num_per_tokens', [32, 128])
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_tokens', [128, 384])
+def test_transposing_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, num_per_tokens):
+    """tkq_per_channel_cast_and_transpose: the transposed data and the [tokens / n, hidden] scales."""
+    from tilekernels_b200 import _lib
+    x = torch.randn((num_tokens, hidden), generator=torch.Generator().manual_seed(43 + num_tokens + hidden)).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(x, 'e4m3', (num_per_tokens, 1))
+    out = Guarded(num_tokens * hidden, cuda_device)
+    sf = Guarded(num_tokens // num_per_tokens * hidden * 4, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_per_channel_cast_and_transpose(xd.data_ptr(), num_tokens, hidden, num_per_tokens, 0, out.ptr, sf.ptr, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref.T.contiguous()), 'transposing cast data')
+    sf.check(_raw(sf_ref), 'transposing cast scales')
+
+
+@pytest.mark.parametrize('hidden', [64, 576])
+@pytest.mark.parametrize('num_out', [16, 144, 400])
+def test_gathering_channel_cast_guard_bands(oracle, cuda_device, num_out, hidden):
+    """tkq_per_channel_cast_fused with pos_to_token: output rows in multiples of 16 (a partial last band of 128), negative
+    entries give rows of zeros."""
+    from tilekernels_b200 import _lib
+    gen = torch.Generator().manual_seed(47 + num_out + hidden)
+    num_in = 200
+    x = torch.randn((num_in, hidden), generator=gen).to(torch.bfloat16)
+    pos = torch.randint(0, num_in, (num_out,), generator=gen, dtype=torch.int32)
+    pos[::7] = -1
+    out_ref, sf_ref = oracle.per_channel_cast_fused(x, 128, None, False, pos)
+    nm = _ceil_div(num_out, 128)
+    out, sf = Guarded(num_out * hidden, cuda_device), Guarded(nm * hidden * 4, cuda_device)
+    xd, pd = x.to(cuda_device), pos.to(cuda_device)
+    rc = _lib.lib().tkq_per_channel_cast_fused(xd.data_ptr(), 0, None, pd.data_ptr(), num_in, num_out, hidden, 0, out.ptr, sf.ptr, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref), 'gathering per-channel cast data')
+    sf.check(_raw(sf_ref), 'gathering per-channel cast scales')
