@@ -9,7 +9,7 @@ backward + cast on cfg3's tensor quantised with power-of-two scales), expand (ro
 ue8m0 scales to 8 positions per token), requant (per-token e4m3 cast of cfg4's tensor already quantised per 128x128 block
 with ue8m0 scales), large_block / large_channel (the tile casts on cfg4's [32768, 7168] tensor), lossless (cfg4's tensor
 as FP4 with 1x32 ue8m0 scales re-blocked to FP8 128x128), swiglu_channel (SwiGLU + per-channel cast + transpose on cfg3's
-tensor).  --rows limits the row count (same per-row distribution).
+tensor), channel_fp8 (fused per-channel cast of cfg4's tensor as FP8 with fp32 group-128 scales).  --rows limits the row count (same per-row distribution).
 """
 import argparse
 
@@ -36,6 +36,7 @@ OPS = {
     'large_block': ('cfg4', lambda x: quant.per_block_cast(x, 'e4m3', (128, 128))),
     'large_channel': ('cfg4', lambda x: quant.per_channel_cast(x, 'e4m3', 128)),
     'lossless': ('cfg4', lambda q: quant.per_block_cast_lossless(q, 'e4m3', (1, 32), (128, 128), True, True, True)),
+    'channel_fp8': ('cfg4', lambda q: quant.per_channel_cast_fused(q, 'e4m3', 128, False, 128)),
     'swiglu_channel': ('cfg3', lambda x: quant.swiglu_forward_and_per_channel_cast_and_transpose(x, 'e4m3', 128)),
 }
 
@@ -49,6 +50,8 @@ def main() -> None:
     cfg, op = OPS[args.op]
     x = make_config_input(cfg, args.rows).cuda()
     if args.op == 'back_e4m3':
+        x = quant.per_token_cast(x, 'e4m3', 128)
+    elif args.op == 'channel_fp8':
         x = quant.per_token_cast(x, 'e4m3', 128)
     elif args.op == 'lossless':
         x = quant.per_token_cast(x, 'e2m1', 32, None, True, True, True)
