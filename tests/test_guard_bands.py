@@ -347,3 +347,67 @@ def test_gathering_channel_cast_guard_bands(oracle, cuda_device, num_out, hidden
     torch.cuda.synchronize()
     out.check(_raw(out_ref), 'gathering per-channel cast data')
     sf.check(_raw(sf_ref), 'gathering per-channel cast scales')
+
+
+@pytest.mark.parametrize('group', [32, 128])
+@pytest.mark.parametrize('hidden', [128, 384])
+@pytest.mark.parametrize('num_tokens,num_topk,num_pad', [(1, 1, 0), (37, 2, 5), (130, 3, 9)])
+def test_swiglu_backward_guard_bands(oracle, cuda_device, num_tokens, num_topk, num_pad, hidden, group):
+    """tkq_swiglu_backward_and_per_token_cast: its four row-shaped outputs (bf16 activation, FP8 gradient with scales,
+    bf16 gradient) inside guard bands; weight_grad (a sum in another order) is compared in the kernel's own test."""
+    from tilekernels_b200 import _lib
+    gen = torch.Generator().manual_seed(53 + num_tokens + hidden + group)
+    entries = num_tokens * num_topk
+    routed = torch.rand(entries, generator=gen) > 0.2
+    num_routed = int(routed.sum().item())
+    rows = num_routed + num_pad
+    if rows == 0:
+        pytest.skip('nothing routed')
+    positions = torch.randperm(rows, generator=gen)[:num_routed].to(torch.int32)
+    t2p = torch.full((entries,), -1, dtype=torch.int32)
+    t2p[routed] = positions
+    pos = torch.full((rows,), -1, dtype=torch.int32)
+    pos[positions.long()] = torch.nonzero(routed).flatten().to(torch.int32)
+    t2p = t2p.view(num_tokens, num_topk)
+    xb = (torch.randn((rows, 2 * hidden), generator=gen) * 2).to(torch.bfloat16)
+    q, qsf = oracle.cast(xb, 'e4m3', (1, group))
+    d = torch.randn((rows, hidden), generator=gen).to(torch.bfloat16)
+    w = torch.rand((num_tokens, num_topk), generator=gen)
+    out_ref, x_grad_ref, _ = oracle.swiglu_backward((q, qsf), d, w, pos, t2p, group, None)
+    fp8_ref, sf_ref = oracle.cast(x_grad_ref, 'e4m3', (1, group), round_sf=True)
+    out = Guarded(rows * hidden * 2, cuda_device)
+    fp8 = Guarded(rows * 2 * hidden, cuda_device)
+    sf = Guarded(rows * (2 * hidden // group) * 4, cuda_device)
+    x_grad = Guarded(rows * 2 * hidden * 2, cuda_device)
+    w_grad = torch.zeros((num_tokens, num_topk), dtype=torch.float32, device=cuda_device)
+    qd, sd, dd, wd, pd, td = (t.contiguous().to(cuda_device) for t in (q, qsf, d, w, pos, t2p))
+    rc = _lib.lib().tkq_swiglu_backward_and_per_token_cast(qd.data_ptr(), sd.data_ptr(), dd.data_ptr(), wd.data_ptr(), pd.data_ptr(), td.data_ptr(),
+                                                           rows, hidden, num_tokens, num_topk, group, -1.0, 1, out.ptr, fp8.ptr, sf.ptr, x_grad.ptr,
+                                                           w_grad.data_ptr(), None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref.bfloat16()), 'backward activation')
+    x_grad.check(_raw(x_grad_ref.bfloat16()), 'backward gradient (bf16)')
+    fp8.check(_raw(fp8_ref), 'backward gradient (FP8)')
+    sf.check(_raw(sf_ref), 'backward gradient scales')
+
+
+@pytest.mark.parametrize('transpose', [0, 1])
+@pytest.mark.parametrize('num_per_tokens', [32, 128])
+@pytest.mark.parametrize('hidden', [64, 320])
+@pytest.mark.parametrize('num_tokens', [128, 384])
+def test_swiglu_channel_cast_guard_bands(oracle, cuda_device, num_tokens, hidden, num_per_tokens, transpose):
+    """tkq_swiglu_forward_and_per_channel_cast: the bf16-rounded activation cast per (n tokens x 1 channel), plain or
+    transposed."""
+    from tilekernels_b200 import _lib
+    x = torch.randn((num_tokens, 2 * hidden), generator=torch.Generator().manual_seed(59 + num_tokens + hidden)).to(torch.bfloat16)
+    act = oracle.swiglu_forward(x).to(torch.bfloat16)
+    out_ref, sf_ref = oracle.cast(act, 'e4m3', (num_per_tokens, 1))
+    out = Guarded(num_tokens * hidden, cuda_device)
+    sf = Guarded(num_tokens // num_per_tokens * hidden * 4, cuda_device)
+    xd = x.to(cuda_device)
+    rc = _lib.lib().tkq_swiglu_forward_and_per_channel_cast(xd.data_ptr(), num_tokens, hidden, num_per_tokens, transpose, -1.0, 0, out.ptr, sf.ptr, None)
+    assert rc == 0, _lib.lib().tkq_last_error_string()
+    torch.cuda.synchronize()
+    out.check(_raw(out_ref.T.contiguous() if transpose else out_ref), 'SwiGLU per-channel cast data')
+    sf.check(_raw(sf_ref), 'SwiGLU per-channel cast scales')
