@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from ..quant.common import current_stream_ptr
+from ..quant.common import current_stream_ptr, device_guard
 from ..quant.types import QuantTensor
 from ..utils import align, ceil_div
 
@@ -35,10 +35,11 @@ def expand_to_fused(x: torch.Tensor, token_topk_to_pos: torch.Tensor, pos_to_exp
 
     out = torch.empty((num_expanded_tokens, hidden), dtype=x.dtype, device=x.device)
     if num_tokens > 0:
-        _lib.check(_lib.lib().tkq_expand_to_fused(
-            x.data_ptr(), num_tokens, hidden * x.element_size(), None, 0, token_topk_to_pos.data_ptr(), num_topk,
-            pos_to_expert.data_ptr(), num_expanded_tokens, 0, out.data_ptr(), None, 0, current_stream_ptr(x.device)),
-            'expand_to_fused')
+        with device_guard(x.device):
+            _lib.check(_lib.lib().tkq_expand_to_fused(
+                x.data_ptr(), num_tokens, hidden * x.element_size(), None, 0, token_topk_to_pos.data_ptr(), num_topk,
+                pos_to_expert.data_ptr(), num_expanded_tokens, 0, out.data_ptr(), None, 0, current_stream_ptr(x.device)),
+                'expand_to_fused')
     return out
 
 
@@ -86,9 +87,10 @@ def expand_to_fused_with_sf(
     sf_shape = (hidden_sf, num_expanded_sf_tokens) if use_tma_aligned_col_major_sf else (num_expanded_tokens, hidden_sf)
     out_sf = torch.empty(sf_shape, dtype=x_sf.dtype, device=x.device)
     if num_tokens > 0:
-        _lib.check(_lib.lib().tkq_expand_to_fused(
-            x.data_ptr(), num_tokens, hidden * x.element_size(), x_sf.data_ptr(), hidden_sf, token_topk_to_pos.data_ptr(),
-            num_topk, pos_to_expert.data_ptr(), num_expanded_tokens, _lib.SF_COL_MAJOR if use_tma_aligned_col_major_sf else 0,
-            out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device)), 'expand_to_fused_with_sf')
+        with device_guard(x.device):
+            _lib.check(_lib.lib().tkq_expand_to_fused(
+                x.data_ptr(), num_tokens, hidden * x.element_size(), x_sf.data_ptr(), hidden_sf, token_topk_to_pos.data_ptr(),
+                num_topk, pos_to_expert.data_ptr(), num_expanded_tokens, _lib.SF_COL_MAJOR if use_tma_aligned_col_major_sf else 0,
+                out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device)), 'expand_to_fused_with_sf')
     out_sf = out_sf[:, :num_expanded_tokens].T if use_tma_aligned_col_major_sf else out_sf
     return out, out_sf

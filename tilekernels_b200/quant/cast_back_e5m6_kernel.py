@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from .common import CastInputConfig, current_stream_ptr, get_cast_input_and_config
+from .common import CastInputConfig, current_stream_ptr, get_cast_input_and_config, device_guard
 from .types import QuantTensor
 
 
@@ -11,7 +11,7 @@ def launch_cast_back(data: torch.Tensor, in_fmt: int, x_sf: torch.Tensor, in_con
     """Allocate the output and enqueue tkq_cast_back; `x_sf` is the scale storage get_cast_input_and_config returns."""
     out = torch.empty((num_tokens, hidden), dtype=torch.bfloat16 if fmt == 'bf16' else torch.float32, device=data.device)
     if num_tokens > 0:
-        with torch.cuda.device(data.device):
+        with device_guard(data.device):
             rc = _lib.lib().tkq_cast_back(data.data_ptr(), in_fmt, x_sf.data_ptr(), in_config.flags, x_sf.stride(0),
                                           in_config.sf_block[0], in_config.sf_block[1], num_tokens, hidden,
                                           _lib.DT_BF16 if fmt == 'bf16' else _lib.DT_FP32, out.data_ptr(),

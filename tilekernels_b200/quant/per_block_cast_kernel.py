@@ -5,7 +5,7 @@ import torch
 
 from .. import _lib
 from ..utils import ceil_div
-from .common import (DTYPE_TO_ENUM, FMT_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr,
+from .common import (device_guard, DTYPE_TO_ENUM, FMT_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr,
                      get_cast_input_and_config, get_cast_output_config)
 from .types import QuantTensor
 
@@ -37,7 +37,7 @@ def per_block_cast_impl(
     out = torch.empty((num_tokens, hidden if fmt == 'e4m3' else hidden // 2), dtype=out_config.torch_dtype, device=x.device)
     out_sf = sf if sf is not None else alloc_scaling_factors((num_tokens, hidden), out_config=out_config, device=x.device)
     if num_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             rc = _lib.lib().tkq_per_block_cast(
                 x.data_ptr(), DTYPE_TO_ENUM[x.dtype], num_tokens, hidden, FMT_TO_ENUM[fmt], block_size[0], block_size[1],
                 flags, out.data_ptr(), out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))

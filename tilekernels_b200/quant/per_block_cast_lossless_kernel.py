@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from .common import (alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_input_and_config, get_cast_output_config,
+from .common import (device_guard, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_input_and_config, get_cast_output_config,
                      get_logical_hidden)
 from .types import QuantTensor
 
@@ -39,7 +39,7 @@ def per_block_cast_lossless(
     out = torch.empty((num_tokens, hidden), dtype=out_config.torch_dtype, device=data.device)
     out_sf = alloc_scaling_factors((num_tokens, hidden), out_config=out_config, device=data.device)
     if num_tokens > 0:
-        with torch.cuda.device(data.device):
+        with device_guard(data.device):
             rc = _lib.lib().tkq_per_block_cast_lossless(
                 data.data_ptr(), x_sf.data_ptr(), in_config.flags, x_sf.stride(0), x_block_size[0], x_block_size[1], num_tokens,
                 hidden, get_logical_hidden(data.stride(0), data.dtype), out_block_size[0], out_block_size[1],

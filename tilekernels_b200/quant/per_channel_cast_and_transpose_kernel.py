@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from .common import current_stream_ptr
+from .common import current_stream_ptr, device_guard
 from .types import QuantTensor
 
 
@@ -23,7 +23,7 @@ def per_channel_cast_and_transpose(x: torch.Tensor, fmt: str, num_per_tokens: in
     out = torch.empty((hidden, num_tokens), dtype=torch.float8_e4m3fn, device=x.device)
     out_sf = torch.empty((num_tokens // num_per_tokens, hidden), dtype=torch.float32, device=x.device)
     if num_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             rc = _lib.lib().tkq_per_channel_cast_and_transpose(x.data_ptr(), num_tokens, hidden, num_per_tokens,
                                                                _lib.ROUND_SF if round_sf else 0, out.data_ptr(), out_sf.data_ptr(),
                                                                current_stream_ptr(x.device))

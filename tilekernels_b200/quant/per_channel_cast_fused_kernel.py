@@ -5,7 +5,7 @@ import torch
 
 from .. import _lib
 from ..utils import ceil_div
-from .common import DTYPE_TO_ENUM, current_stream_ptr
+from .common import DTYPE_TO_ENUM, current_stream_ptr, device_guard
 from .types import QuantTensor
 
 _IN_FP8 = 2  # input kind of tkq_per_channel_cast_fused next to the bf16 / fp32 enums
@@ -69,7 +69,7 @@ def per_channel_cast_fused(
     out_sf = torch.empty((ceil_div(num_tokens_out, num_per_tokens), hidden), dtype=torch.float32, device=x.device)
     if num_tokens_out > 0:
         flags = _lib.ROUND_SF if round_sf else 0
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             if x_sf is None and pos_to_token is None:  # rectangular input: the TMA tile pipeline
                 rc = _lib.lib().tkq_per_channel_cast(x.data_ptr(), in_kind, num_tokens, hidden, flags, out.data_ptr(),
                                                      out_sf.data_ptr(), current_stream_ptr(x.device))

@@ -4,7 +4,7 @@ from typing import Optional, Union
 import torch
 
 from .. import _lib
-from .common import (DTYPE_TO_ENUM, FMT_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr,
+from .common import (device_guard, DTYPE_TO_ENUM, FMT_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr,
                      get_cast_input_and_config, get_cast_output_config, get_logical_hidden, get_physical_hidden)
 from .per_token_cast_to_e5m6_kernel import per_token_cast_to_e5m6
 from .types import QuantTensor
@@ -55,7 +55,7 @@ def per_token_cast_impl(
                       device=x.device)
     out_sf = sf if sf is not None else alloc_scaling_factors((num_tokens, hidden), out_config=out_config, device=x.device)
     if num_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             if in_config.with_sf:
                 rc = _lib.lib().tkq_per_token_cast_quantized(
                     x.data_ptr(), _lib.FMT_E4M3 if x.dtype == torch.float8_e4m3fn else _lib.FMT_E2M1, x_sf.data_ptr(),

@@ -2,7 +2,7 @@
 import torch
 
 from .. import _lib
-from .common import (DTYPE_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_input_and_config,
+from .common import (device_guard, DTYPE_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_input_and_config,
                      get_cast_output_config)
 from .types import QuantTensor
 
@@ -35,7 +35,7 @@ def per_token_cast_to_e5m6(
     out = torch.empty((num_tokens, hidden // 8 * 3), dtype=torch.uint32, device=x.device)
     out_sf = alloc_scaling_factors((num_tokens, hidden), out_config=out_config, device=x.device)
     if num_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             rc = _lib.lib().tkq_per_token_cast_e5m6(
                 x.data_ptr(), DTYPE_TO_ENUM[x.dtype], num_tokens, hidden, x.stride(0), out_config.flags, out.data_ptr(),
                 out_sf.data_ptr(), out_sf.stride(0), current_stream_ptr(x.device))

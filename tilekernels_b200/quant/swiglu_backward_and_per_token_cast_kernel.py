@@ -5,7 +5,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from .common import current_stream_ptr
+from .common import current_stream_ptr, device_guard
 from .types import QuantTensor
 
 
@@ -68,11 +68,12 @@ def swiglu_backward_and_per_token_cast(
     weight_grad = torch.empty((num_tokens, num_topk), dtype=torch.float32, device=x.device)
 
     if num_expand_tokens > 0:
-        _lib.check(_lib.lib().tkq_swiglu_backward_and_per_token_cast(
-            x.data_ptr(), x_sf.data_ptr(), grad_out.data_ptr(), weight.data_ptr(), pos_to_token_topk.data_ptr(),
-            token_topk_to_pos.data_ptr(), num_expand_tokens, hidden, num_tokens, num_topk, num_per_channels,
-            -1.0 if swiglu_clamp_value is None else float(swiglu_clamp_value), _lib.ROUND_SF if round_sf else 0,
-            out.data_ptr(), x_grad_fp8.data_ptr(), x_grad_fp8_sf.data_ptr(), x_grad.data_ptr(), weight_grad.data_ptr(),
-            current_stream_ptr(x.device)), 'swiglu_backward_and_per_token_cast')
+        with device_guard(x.device):
+            _lib.check(_lib.lib().tkq_swiglu_backward_and_per_token_cast(
+                x.data_ptr(), x_sf.data_ptr(), grad_out.data_ptr(), weight.data_ptr(), pos_to_token_topk.data_ptr(),
+                token_topk_to_pos.data_ptr(), num_expand_tokens, hidden, num_tokens, num_topk, num_per_channels,
+                -1.0 if swiglu_clamp_value is None else float(swiglu_clamp_value), _lib.ROUND_SF if round_sf else 0,
+                out.data_ptr(), x_grad_fp8.data_ptr(), x_grad_fp8_sf.data_ptr(), x_grad.data_ptr(), weight_grad.data_ptr(),
+                current_stream_ptr(x.device)), 'swiglu_backward_and_per_token_cast')
 
     return out, (x_grad_fp8, x_grad_fp8_sf), x_grad, weight_grad

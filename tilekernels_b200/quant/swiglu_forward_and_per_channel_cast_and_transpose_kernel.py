@@ -5,7 +5,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from .common import current_stream_ptr
+from .common import current_stream_ptr, device_guard
 from .types import QuantTensor
 
 
@@ -39,7 +39,7 @@ def swiglu_forward_and_per_channel_cast_and_transpose(
     out = torch.empty((num_tokens, hidden) if without_transpose else (hidden, num_tokens), dtype=torch.float8_e4m3fn, device=x.device)
     out_sf = torch.empty((num_tokens // num_per_tokens, hidden), dtype=torch.float32, device=x.device)
     if num_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             rc = _lib.lib().tkq_swiglu_forward_and_per_channel_cast(
                 x.data_ptr(), num_tokens, hidden, num_per_tokens, 0 if without_transpose else 1,
                 -1.0 if swiglu_clamp_value is None else float(swiglu_clamp_value), _lib.ROUND_SF if round_sf else 0,

@@ -6,7 +6,7 @@ import torch
 
 from .. import _lib
 from ..config import get_exact_swiglu_codes, get_num_sms
-from .common import DTYPE_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_output_config
+from .common import DTYPE_TO_ENUM, alloc_scaling_factors, cast_epilogue, current_stream_ptr, get_cast_output_config, device_guard
 from .types import QuantTensor
 
 
@@ -68,7 +68,7 @@ def swiglu_forward_and_per_token_cast(
     out = torch.empty((num_expanded_tokens, hidden), dtype=torch.float8_e4m3fn, device=x.device)
     out_sf = alloc_scaling_factors((num_expanded_tokens, hidden), out_config, device=x.device)
     if num_expanded_tokens > 0:
-        with torch.cuda.device(x.device):
+        with device_guard(x.device):
             rc = _lib.lib().tkq_swiglu_forward_and_per_token_cast(
                 x.data_ptr(), DTYPE_TO_ENUM[x.dtype], num_expanded_tokens, hidden, num_per_channels,
                 None if pos_to_token_topk is None else pos_to_token_topk.data_ptr(),
