@@ -87,6 +87,36 @@ def test_argument_checks_of_the_backward_and_expand_entry_points(lib):
     assert b'expand_to_fused' in lib.tkq_last_error_string()
 
 
+def test_argument_checks_of_the_quantized_input_entry_points(lib):
+    buf = (ctypes.c_char * 4096)()
+    p32 = (ctypes.addressof(buf) + 31) // 32 * 32
+    lossless = lib.tkq_per_block_cast_lossless
+    # (x, x_sf, x_sf_flags, x_sf_stride, x_block_m, x_block_k, tokens, hidden, x_row_stride, out_block_m, out_block_k, flags,
+    #  out, sf, sf_stride, stream)
+    assert lossless(p32, p32, 0, 8, 1, 32, 0, 256, 256, 128, 128, 0, p32, p32, 2, None) == 0          # no tokens
+    assert lossless(p32, p32, 0, 8, 1, 32, 4, 256, 256, 64, 128, 0, p32, p32, 2, None) == -2         # output block 64 x 128
+    assert lossless(p32, p32, 0, 8, 1, 32, 4, 240, 240, 128, 128, 0, p32, p32, 2, None) == -2        # hidden % 32
+    assert lossless(p32, p32, 0, 8, 32, 32, 4, 256, 256, 1, 128, 0, p32, p32, 2, None) == -2         # output block below the input block
+    assert lossless(p32, p32, 0, 8, 1, 32, 4, 256, 256, 128, 128, 4, p32, p32, 16, None) == -2       # packed scales, not column-major
+    assert lossless(p32 + 8, p32, 0, 8, 1, 32, 4, 256, 256, 128, 128, 0, p32, p32, 2, None) == -3    # rows on 8-byte boundaries only
+    assert lossless(p32, p32, 0, 8, 1, 32, 4, 256, 272, 128, 128, 0, p32, p32, 2, None) == -3        # row stride of 136 bytes
+    assert b'per_block_cast_lossless' in lib.tkq_last_error_string()
+    assert lossless(p32, None, 0, 8, 1, 32, 4, 256, 256, 128, 128, 0, p32, p32, 2, None) == -1       # null
+    requant = lib.tkq_per_token_cast_quantized
+    # (x, in_fmt, x_sf, x_sf_flags, x_sf_stride, x_block_m, x_block_k, tokens, hidden, x_row_stride, fmt, group, flags, out, sf,
+    #  sf_stride, stream)
+    assert requant(p32, 0, p32, 0, 2, 128, 128, 0, 256, 256, 0, 128, 0, p32, p32, 2, None) == 0      # no tokens
+    assert requant(p32, 2, p32, 0, 2, 128, 128, 4, 256, 256, 0, 128, 0, p32, p32, 2, None) == -1     # E5M6 is not an input format
+    assert requant(p32, 0, p32, 0, 2, 128, 128, 4, 256, 256, 0, 256, 0, p32, p32, 2, None) == -2     # one scale per token
+    assert requant(p32, 0, p32, 4, 2, 128, 128, 4, 256, 256, 0, 128, 0, p32, p32, 2, None) == -2     # packed input scales, not column-major
+    back = lib.tkq_cast_back
+    # (x, in_fmt, x_sf, x_sf_flags, x_sf_stride, x_block_m, x_block_k, tokens, hidden, out_dtype, out, stream)
+    assert back(p32, 0, p32, 0, 2, 1, 128, 0, 256, 0, p32, None) == 0                                 # no tokens
+    assert back(p32, 0, p32, 0, 2, 1, 128, 4, 250, 0, p32, None) == -2                                # hidden % 16
+    assert back(p32, 0, p32, 0, 2, 1, 128, 4, 256, 5, p32, None) == -1                                # output type
+    assert back(p32 + 4, 0, p32, 0, 2, 1, 128, 4, 256, 0, p32, None) == -3                            # alignment
+
+
 @pytest.mark.gpu
 def test_bounded_wait_gives_up_and_reports(oracle, cuda_device):
     """The waits on asynchronous copies are bounded.  The self-test kernel receives one real copy, then waits a few
