@@ -280,6 +280,12 @@ def op_specs(torch, quant, moe, device) -> list:
              lambda x: quant.per_token_cast(x, 'e5m6', x.shape[1]), fmt='e5m6', out='bf16'),
         spec('per_token_cast', 'cfg4 requantise', 'cfg4', lambda q: quant.per_token_cast(q, 'e4m3', 128, (128, 128), **ue),
              lambda x: quant.per_block_cast(x, 'e4m3', (128, 128), **ue), fmt='e4m3', group=128, x='e4m3 128x128 ue8m0'),
+        spec('per_token_cast', 'cfg4 requantise, fp32 scales', 'cfg4', lambda q: quant.per_token_cast(q, 'e4m3', 128, (1, 128)),
+             lambda x: quant.per_token_cast(x, 'e4m3', 128), fmt='e4m3', group=128, x='e4m3 1x128 fp32 scales'),
+        spec('per_token_cast', 'cfg4 requantise, FP4 input', 'cfg4', lambda q: quant.per_token_cast(q, 'e4m3', 128, (1, 32), **ue),
+             lambda x: quant.per_token_cast(x, 'e2m1', 32, None, **ue), fmt='e4m3', group=128, x='e2m1 1x32 ue8m0'),
+        spec('per_channel_cast_fused', 'cfg4 FP8 input', 'cfg4', lambda q: quant.per_channel_cast_fused(q, 'e4m3', 128, False, 128),
+             lambda x: quant.per_token_cast(x, 'e4m3', 128), fmt='e4m3', x='e4m3 1x128 fp32 scales'),
         spec('per_channel_cast_fused', 'cfg2 gather', 'cfg2', lambda x: quant.per_channel_cast_fused(x, 'e4m3', 128, False, None, gathers[x.shape[0]]),
              fmt='e4m3', rows_out=8192),
         spec('per_channel_cast_and_transpose', 'cfg2', 'cfg2', lambda x: quant.per_channel_cast_and_transpose(x, 'e4m3', 128), fmt='e4m3', block='128x1'),
