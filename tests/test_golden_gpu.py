@@ -289,3 +289,22 @@ def test_swiglu_against_torch_on_the_device(oracle, cuda_device):
         # ones); loose sanity bounds only, the counts are what this test is for
         assert d['code_max_step'] <= 1 and d['codes_differing'] <= 1e-4 * d['codes'], d
         assert d['scale_max_ulp'] <= 4 and d['scales_differing'] <= (0 if rnd else 0.1 * d['scales']), d
+
+
+@pytest.mark.parametrize('flags', [(False, False, False), (True, True, True)], ids=flags_id)
+def test_swiglu_full_size_benchmark_workload(oracle, cuda_device, flags):
+    """The whole cfg3 workload ([16384, 2 x 2048]: 33.5 M activations, 262144 groups) against the oracle: every scale
+    identical, FP8 codes at most one step apart on at most 1e-4 of the elements, dequantised values of equal codes
+    within 1e-3."""
+    from helpers import swiglu_cast_differences
+    from tilekernels_b200 import quant
+    col, rnd, ue = flags
+    kw = dict(use_tma_aligned_col_major_sf=col, round_sf=rnd, use_packed_ue8m0=ue)
+    x = make_config_input('cfg3')
+    out, sf = quant.swiglu_forward_and_per_token_cast(x.to(cuda_device), 'e4m3', 128, **kw)
+    out_ref, sf_ref = oracle.cast(oracle.swiglu_forward(x), 'e4m3', (1, 128), **kw)
+    d = swiglu_cast_differences(to_host(out), to_host(sf), out_ref, sf_ref, 128, oracle.sf_to_float)
+    print(f'cfg3 full size {flags_id(flags)}, kernel vs oracle:', d)
+    assert d['scales'] == 16384 * 16 and d['scales_differing'] == 0, d
+    assert d['code_max_step'] <= 1 and d['codes_differing'] <= 1e-4 * d['codes'], d
+    assert d['dequant_max_rel_equal_codes'] <= 1e-3, d
